@@ -30,7 +30,7 @@ from typing import Callable, Hashable
 
 import torch
 
-from ..parts.base import CacheSpec, LayerCache
+from ..parts.base import CacheSpec, LayerCache, spec_members
 from .allocator import OutOfPages, PageAllocator
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -49,11 +49,13 @@ class _RequestPages:
 class PageGroup:
     """One layer group's pages."""
 
-    def __init__(self, index: int, spec: CacheSpec, entries: list[int], page_size: int,
+    def __init__(self, index: int, spec: CacheSpec, entries: list, page_size: int,
                  num_pages: int, dtype: torch.dtype, device: torch.device | None):
         self.index = index
         self.spec = spec
-        self.entries = entries
+        # (cache entry, member of a composite spec) pairs, or plain entry numbers
+        self.members = [x if isinstance(x, tuple) else (x, 0) for x in entries]
+        self.entries = [e for e, _ in self.members]
         self.page_size = page_size = int(getattr(spec, "page_size", None) or page_size)
         self.page_shape = tuple(spec.page_shape(page_size))
         self.window = getattr(spec, "window", None)
@@ -105,29 +107,33 @@ class CacheManager:
 
         # group cache entries by identical paged spec, in order of first appearance
         self.groups: list[PageGroup] = []
-        self._entry_group: dict[int, tuple[int, int]] = {}  # entry -> (group, index in group)
-        by_spec: dict[CacheSpec, list[int]] = {}
-        for e, spec in enumerate(self.specs):
-            if spec is None:
-                continue
-            if spec.storage == "pages":
-                by_spec.setdefault(spec, []).append(e)
-            elif spec.storage != "slots":
-                raise ValueError(f"cache entry {e}: storage {spec.storage!r} is neither "
-                                 f"'pages' nor 'slots'")
+        # a cache entry is one spec or a composite of several; (entry, member) names one of them
+        self._entry_group: dict[tuple[int, int], tuple[int, int]] = {}  # -> (group, index in group)
+        by_spec: dict[CacheSpec, list[tuple[int, int]]] = {}
+        for e, whole in enumerate(self.specs):
+            for j, spec in enumerate(spec_members(whole)):
+                if spec.storage == "pages":
+                    by_spec.setdefault(spec, []).append((e, j))
+                elif spec.storage != "slots":
+                    raise ValueError(f"cache entry {e}: storage {spec.storage!r} is neither "
+                                     f"'pages' nor 'slots'")
         for gi, (spec, entries) in enumerate(by_spec.items()):
             n = num_pages[gi] if isinstance(num_pages, dict) else num_pages
             self.groups.append(PageGroup(gi, spec, entries, page_size, n, dtype, self.device))
-            for k, e in enumerate(entries):
-                self._entry_group[e] = (gi, k)
+            for k, key in enumerate(entries):
+                self._entry_group[key] = (gi, k)
 
-        # fixed-size state: one tensor per cache entry that asks for it
+        # fixed-size state: one tensor per cache entry (or member of one) that asks for it
         self.scratch_slot = max_requests
-        self.state: dict[int, torch.Tensor] = {}
-        for e, spec in enumerate(self.specs):
-            if spec is not None and spec.storage == "slots" and self.device is not None:
-                self.state[e] = torch.zeros((max_requests + 1, *spec.slot_shape()),
-                                            dtype=_STATE_DTYPES[spec.dtype], device=self.device)
+        # keyed by the entry's number, or by (entry, member) inside a composite spec
+        self.state: dict = {}
+        for e, whole in enumerate(self.specs):
+            composite = whole is not None and whole.storage == "composite"
+            for j, spec in enumerate(spec_members(whole)):
+                if spec.storage == "slots" and self.device is not None:
+                    self.state[(e, j) if composite else e] = torch.zeros((max_requests + 1, *spec.slot_shape()),
+                                                     dtype=_STATE_DTYPES[spec.dtype],
+                                                     device=self.device)
         self._free_slots: list[int] = list(range(max_requests))
         heapq.heapify(self._free_slots)
         self._slot_of: dict[Hashable, int] = {}
@@ -256,18 +262,24 @@ class CacheManager:
 
     def layer_caches(self) -> list[LayerCache | None]:
         """One view per cache entry, in entry order."""
-        out: list[LayerCache | None] = []
-        for e, spec in enumerate(self.specs):
-            if spec is None:
-                out.append(None)
-            elif spec.storage == "pages":
-                gi, k = self._entry_group[e]
+        def view(e: int, j: int, spec) -> LayerCache:
+            if spec.storage == "pages":
+                gi, k = self._entry_group[(e, j)]
                 g = self.groups[gi]
-                out.append(LayerCache(spec, group=gi,
-                                      pool=None if g.pool is None else g.pool[k],
-                                      page_size=g.page_size))
+                return LayerCache(spec, group=gi, pool=None if g.pool is None else g.pool[k],
+                                  page_size=g.page_size)
+            composite = self.specs[e].storage == "composite"
+            return LayerCache(spec, state=self.state.get((e, j) if composite else e))
+
+        out: list[LayerCache | None] = []
+        for e, whole in enumerate(self.specs):
+            if whole is None:
+                out.append(None)
+            elif whole.storage == "composite":
+                out.append(LayerCache(whole, members=[view(e, j, spec) for j, spec
+                                                      in enumerate(spec_members(whole))]))
             else:
-                out.append(LayerCache(spec, state=self.state.get(e)))
+                out.append(view(e, 0, whole))
         return out
 
     # ---------------------------------------------------------- accounting

@@ -1,6 +1,7 @@
 """One registry from an architecture's name to its configuration class and model plan.
 
-The name is ``config.json["architectures"][0]``.  The reference has no
+The name is ``config.json["architectures"][0]``, or ``config.json["architecture"]`` where a
+checkpoint names its design with one string.  The reference has no
 registry: every entry point imports ``LlamaModel`` by name and ignores
 config.json (``model/llama.py:335``, ``generate.py:273``).
 """
@@ -19,15 +20,21 @@ from .model_config import ConfigError, ModelConfig
 class Architecture:
     name: str
     config_class: type[ModelConfig]
-    plan: Callable[[Any], Any]  # typed config -> models.plan.ModelPlan
+    plan: Callable[..., Any]  # typed config -> models.plan.ModelPlan
+    # True: some sizes are given by the checkpoint's tensor shapes alone; ``plan`` then takes
+    # ``tensor_shapes`` (name -> shape of what the checkpoint holds, or None without one)
+    reads_shapes: bool = False
+
+    def plan_for(self, cfg: Any, tensor_shapes: dict[str, tuple[int, ...]] | None = None) -> Any:
+        return self.plan(cfg, tensor_shapes) if self.reads_shapes else self.plan(cfg)
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
 def register_architecture(name: str, config_class: type[ModelConfig],
-                          plan: Callable[[Any], Any]) -> None:
-    _ARCHITECTURES[name] = Architecture(name, config_class, plan)
+                          plan: Callable[..., Any], reads_shapes: bool = False) -> None:
+    _ARCHITECTURES[name] = Architecture(name, config_class, plan, reads_shapes)
 
 
 def known_architectures() -> list[str]:
@@ -42,9 +49,11 @@ def _load_builtin() -> None:
 def architecture_of(config: dict[str, Any]) -> Architecture:
     _load_builtin()
     names = config.get("architectures")
+    if isinstance(config.get("architecture"), str) and not names:
+        names = [config["architecture"]]
     if not names or not isinstance(names, (list, tuple)):
-        raise ConfigError("config.json has no 'architectures' list; "
-                          f"known architectures: {sorted(_ARCHITECTURES)}")
+        raise ConfigError("config.json has neither an 'architectures' list nor an "
+                          f"'architecture' name; known architectures: {sorted(_ARCHITECTURES)}")
     name = names[0]
     try:
         return _ARCHITECTURES[name]

@@ -1,0 +1,267 @@
+// Generalised delta rule with a matrix state per head, carried from token to token.
+//
+// Per token and head, key channel c and value channel d (D of each):
+//     decay_c = exp(-exp(-1/2) * sigmoid(w0_c + sum_l W2[c,l] tanh(low_l)))
+//     rate_c  = sigmoid(a_c + bias_c)
+//     u       = k / sqrt(sum_c k_c^2 + 1e-6)
+//     S[c,d] <- decay_c S[c,d] - rate_c u_c (sum_c' u_c' S[c',d]) + k_c v_d     (old S on the right)
+//     o_d     = sum_c S[c,d] r_c
+//     y       = o / sqrt(mean_d o_d^2 + eps) * gain * sigmoid(g)
+// The projections r, k, v, g, a, low arrive as columns of one matrix product (activation
+// dtype); everything after them is float32: decays, rates, the unit key, the state, the
+// head-wise norm and the gate.  Three kernels:
+//   prepare     per token, in parallel: decay, u, rate*u as float32
+//   recurrence  per (sequence, head, slice of value channels): the scan over the step's
+//               tokens; the state comes from and returns to the request's slot
+//   output      per token, in parallel: head-wise norm, gain, gate
+// The scan's order is the token order, so a sequence's result is the same however its tokens
+// were cut into steps and whatever else the batch holds.
+#include "common.cuh"
+
+namespace si {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// proj columns: [r | k | v | g | a | low], each of the first five HD = heads*D wide, low L wide.
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride,
+                                     const T* __restrict__ w2, const float* __restrict__ w0,
+                                     const float* __restrict__ a_bias, float* __restrict__ prep,
+                                     int heads, int D, int L) {
+  extern __shared__ float low_s[];  // [L] tanh of the inner projection
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+  const int HD = heads * D;
+  const bool mine = c < D;
+  const int col = h * D + c;
+  // weights first: no kernel of the step writes them
+  const float bias = mine ? a_bias[col] : 0.0f;
+  const float z0 = mine ? w0[col] : 0.0f;
+  pdl_wait();
+  pdl_trigger();
+  const T* row = proj + (size_t)t * proj_stride;
+  for (int l = threadIdx.x; l < L; l += blockDim.x) low_s[l] = tanhf(to_f32<T>(row[5 * HD + l]));
+  const float k = mine ? to_f32<T>(row[HD + col]) : 0.0f;
+  const float ss = block_sum(k * k, red);  // also orders low_s
+  if (!mine) return;
+  float z = z0;
+  const T* w2row = w2 + (size_t)col * L;
+  for (int l = 0; l < L; ++l) z = fmaf(to_f32<T>(w2row[l]), low_s[l], z);
+  const float decay = expf(-0.60653065971263342f * sigmoidf_(z));
+  const float u = k / sqrtf(ss + 1e-6f);
+  const float rate = sigmoidf_(to_f32<T>(row[4 * HD + col]) + bias);
+  float* dst = prep + (size_t)t * 3 * HD + col;
+  dst[0] = decay;
+  dst[HD] = u;
+  dst[2 * HD] = rate * u;
+}
+
+// Threads of a block: DC value channels x KS lanes; lane ks of channel d keeps S[c][d] for
+// c = ks + KS*i, i < R, in registers (c >= D padded with zeros).  Tokens are taken in groups
+// of TB whose inputs are staged in shared memory.
+constexpr int DELTA_KS = 4;    // lanes that share one value channel
+constexpr int DELTA_DC = 32;   // value channels per block
+constexpr int DELTA_TB = 8;    // tokens staged at a time
+
+template <typename T, int R>
+__global__ void __launch_bounds__(DELTA_KS * DELTA_DC)
+delta_recurrence_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ prep,
+                        const int* __restrict__ cu_q, const int* __restrict__ seq_slots,
+                        float* __restrict__ state, float* __restrict__ o_out, int heads, int D) {
+  extern __shared__ float sm[];
+  const int Dp = R * DELTA_KS;                 // padded number of key channels
+  float* in_s = sm;                            // [TB][5][Dp]: decay, u, rate*u, k, r
+  float* v_s = sm + DELTA_TB * 5 * Dp;         // [TB][DC]
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int d0 = blockIdx.z * DELTA_DC;
+  const int tid = threadIdx.x;
+  const int ks = tid % DELTA_KS, dl = tid / DELTA_KS;
+  const int d = d0 + dl;
+  const bool col_ok = d < D;
+  const int HD = heads * D;
+  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
+  const int slot = seq_slots[s];
+  pdl_wait();
+  pdl_trigger();
+  float* S_g = state + ((size_t)slot * heads + h) * D * D;
+  float S[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int c = ks + DELTA_KS * i;
+    S[i] = (col_ok && c < D) ? S_g[(size_t)c * D + d] : 0.0f;
+  }
+  for (int tb = t_begin; tb < t_end; tb += DELTA_TB) {
+    const int nt = min(DELTA_TB, t_end - tb);
+    __syncthreads();  // the previous group's inputs are no longer read
+    for (int idx = tid; idx < nt * 5 * Dp; idx += blockDim.x) {
+      const int c = idx % Dp, which = (idx / Dp) % 5, tt = idx / (5 * Dp);
+      const size_t t = (size_t)(tb + tt);
+      float x = 0.0f;
+      if (c < D) {
+        if (which < 3) x = prep[t * 3 * HD + (size_t)which * HD + h * D + c];
+        else if (which == 3) x = to_f32<T>(proj[t * proj_stride + HD + h * D + c]);
+        else x = to_f32<T>(proj[t * proj_stride + h * D + c]);
+      }
+      in_s[idx] = x;
+    }
+    for (int idx = tid; idx < nt * DELTA_DC; idx += blockDim.x) {
+      const int dd = idx % DELTA_DC, tt = idx / DELTA_DC;
+      v_s[idx] = (d0 + dd < D)
+                     ? to_f32<T>(proj[(size_t)(tb + tt) * proj_stride + 2 * HD + h * D + d0 + dd])
+                     : 0.0f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* w_s = in_s + tt * 5 * Dp;
+      const float* u_s = w_s + Dp;
+      const float* au_s = w_s + 2 * Dp;
+      const float* k_s = w_s + 3 * Dp;
+      const float* r_s = w_s + 4 * Dp;
+      float us0 = 0.0f, us1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < R; i += 2) {
+        us0 = fmaf(u_s[ks + DELTA_KS * i], S[i], us0);
+        if (i + 1 < R) us1 = fmaf(u_s[ks + DELTA_KS * (i + 1)], S[i + 1], us1);
+      }
+      float us = us0 + us1;
+#pragma unroll
+      for (int o = DELTA_KS / 2; o > 0; o >>= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
+      const float v = v_s[tt * DELTA_DC + dl];
+      float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int c = ks + DELTA_KS * i;
+        S[i] = fmaf(w_s[c], S[i], fmaf(k_s[c], v, -au_s[c] * us));
+        if (i & 1) o1 = fmaf(S[i], r_s[c], o1);
+        else o0 = fmaf(S[i], r_s[c], o0);
+      }
+      float o = o0 + o1;
+#pragma unroll
+      for (int off = DELTA_KS / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (ks == 0 && col_ok) o_out[(size_t)(tb + tt) * HD + h * D + d] = o;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int c = ks + DELTA_KS * i;
+    if (col_ok && c < D) S_g[(size_t)c * D + d] = S[i];
+  }
+}
+
+template <typename T, typename TW>
+__global__ void delta_output_kernel(const float* __restrict__ o, const T* __restrict__ proj,
+                                    int proj_stride, const TW* __restrict__ gain, T* __restrict__ out,
+                                    int heads, int D, float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+  const int HD = heads * D;
+  const bool mine = c < D;
+  const int col = h * D + c;
+  const float gn = mine ? to_f32<TW>(gain[col]) : 0.0f;
+  pdl_wait();
+  pdl_trigger();
+  const float x = mine ? o[(size_t)t * HD + col] : 0.0f;
+  const float ss = block_sum(x * x, red);
+  if (!mine) return;
+  const float g = sigmoidf_(to_f32<T>(proj[(size_t)t * proj_stride + 3 * HD + col]));
+  out[(size_t)t * HD + col] = from_f32<T>(x / sqrtf(ss / (float)D + eps) * gn * g);
+}
+
+}  // namespace si
+
+SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2, const float* w0,
+                            const float* a_bias, float* prep, int n_tokens, int heads, int D, int L,
+                            int dtype, cudaStream_t stream) {
+  if (!proj || !w2 || !w0 || !a_bias || !prep || n_tokens < 0 || heads <= 0 || D <= 0 || L <= 0)
+    return SI_ERR_ARG;
+  if (D > 1024 || heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_tokens == 0) return SI_OK;
+  const int threads = (D + 31) / 32 * 32;
+  dim3 grid(n_tokens, heads);
+  const size_t smem = (size_t)L * sizeof(float);
+  if (smem > 48 * 1024) return SI_ERR_TOO_LARGE;
+  if (dtype == SI_BF16)
+    SI_LAUNCH(si::delta_prepare_kernel<__nv_bfloat16>, grid, threads, smem, stream,
+              (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)w2, w0, a_bias, prep,
+              heads, D, L);
+  else if (dtype == SI_F32)
+    SI_LAUNCH(si::delta_prepare_kernel<float>, grid, threads, smem, stream, (const float*)proj,
+              proj_stride, (const float*)w2, w0, a_bias, prep, heads, D, L);
+  else
+    return SI_ERR_DTYPE;
+  return SI_OK;
+}
+
+template <typename T, int R>
+static int launch_delta_recurrence(const void* proj, int proj_stride, const float* prep,
+                                   const int* cu_q, const int* seq_slots, float* state, float* o_out,
+                                   int n_seqs, int heads, int D, cudaStream_t stream) {
+  const size_t smem = (size_t)si::DELTA_TB * (5 * R * si::DELTA_KS + si::DELTA_DC) * sizeof(float);
+  auto kern = si::delta_recurrence_kernel<T, R>;
+  if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
+  dim3 grid(n_seqs, heads, (D + si::DELTA_DC - 1) / si::DELTA_DC);
+  SI_LAUNCH(kern, grid, si::DELTA_KS * si::DELTA_DC, smem, stream, (const T*)proj, proj_stride, prep,
+            cu_q, seq_slots, state, o_out, heads, D);
+  return SI_OK;
+}
+
+template <typename T>
+static int delta_recurrence_by_size(const void* proj, int proj_stride, const float* prep,
+                                    const int* cu_q, const int* seq_slots, float* state, float* o_out,
+                                    int n_seqs, int heads, int D, cudaStream_t stream) {
+  const int r = (D + si::DELTA_KS - 1) / si::DELTA_KS;
+#define SI_DELTA_CASE(R)                                                                        \
+  if (r <= R)                                                                                   \
+    return launch_delta_recurrence<T, R>(proj, proj_stride, prep, cu_q, seq_slots, state, o_out, \
+                                         n_seqs, heads, D, stream);
+  SI_DELTA_CASE(4)
+  SI_DELTA_CASE(8)
+  SI_DELTA_CASE(16)
+  SI_DELTA_CASE(32)
+  SI_DELTA_CASE(64)
+#undef SI_DELTA_CASE
+  return SI_ERR_UNSUPPORTED;  // heads of more than 256 channels
+}
+
+// state: [slots, heads, D, D] float32 (key channel, value channel); sequence s of the step owns
+// the tokens cu_q[s]..cu_q[s+1]-1 and the slot seq_slots[s].  o_out: [n_tokens, heads*D] float32.
+SI_API int si_delta_recurrence(const void* proj, int proj_stride, const float* prep, const int* cu_q,
+                               const int* seq_slots, float* state, float* o_out, int n_seqs,
+                               int heads, int D, int dtype, cudaStream_t stream) {
+  if (!proj || !prep || !cu_q || !seq_slots || !state || !o_out || n_seqs < 0 || heads <= 0 || D <= 0)
+    return SI_ERR_ARG;
+  if (heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_seqs == 0) return SI_OK;
+  if (dtype == SI_BF16)
+    return delta_recurrence_by_size<__nv_bfloat16>(proj, proj_stride, prep, cu_q, seq_slots, state,
+                                                   o_out, n_seqs, heads, D, stream);
+  if (dtype == SI_F32)
+    return delta_recurrence_by_size<float>(proj, proj_stride, prep, cu_q, seq_slots, state, o_out,
+                                           n_seqs, heads, D, stream);
+  return SI_ERR_DTYPE;
+}
+
+SI_API int si_delta_output(const float* o, const void* proj, int proj_stride, const void* gain,
+                           void* out, int n_tokens, int heads, int D, float eps, int dtype,
+                           int gain_dtype, cudaStream_t stream) {
+  if (!o || !proj || !gain || !out || n_tokens < 0 || heads <= 0 || D <= 0 || !(eps > 0.0f))
+    return SI_ERR_ARG;
+  if (D > 1024 || heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_tokens == 0) return SI_OK;
+  const int threads = (D + 31) / 32 * 32;
+  dim3 grid(n_tokens, heads);
+  if (dtype == SI_BF16 && gain_dtype == SI_BF16)
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, __nv_bfloat16>), grid, threads, 0, stream, o,
+              (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)gain, (__nv_bfloat16*)out,
+              heads, D, eps);
+  else if (dtype == SI_BF16 && gain_dtype == SI_F32)
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, float>), grid, threads, 0, stream, o,
+              (const __nv_bfloat16*)proj, proj_stride, (const float*)gain, (__nv_bfloat16*)out, heads,
+              D, eps);
+  else if (dtype == SI_F32 && gain_dtype == SI_F32)
+    SI_LAUNCH((si::delta_output_kernel<float, float>), grid, threads, 0, stream, o,
+              (const float*)proj, proj_stride, (const float*)gain, (float*)out, heads, D, eps);
+  else
+    return SI_ERR_DTYPE;
+  return SI_OK;
+}

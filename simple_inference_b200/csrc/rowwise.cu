@@ -1,7 +1,7 @@
 // Row-wise kernels: embedding gather, RMSNorm with the residual add fused in,
 // and the SwiGLU gate.  All arithmetic is float32; one rounding at the store.
 //
-//   embedding   x0[t] = E[id[t]]                       reference ops/embedding.py:57-60
+//   embedding   x0[t] = scale * E[id[t]]               reference ops/embedding.py:57-60 (scale 1)
 //   RMSNorm     y = x * rsqrt(mean(x^2) + eps) * w     reference ops/rmsnorm.py:41-46,
 //                                                       kernels/rmsnorm_kernel.py:105-113
 //   residual    x = x + h (fused into the norm)        reference model/block.py:138,144
@@ -14,7 +14,7 @@ namespace si {
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int hidden, int vocab) {
+                                    float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
@@ -27,7 +27,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -207,19 +207,85 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
   }
 }
 
+// ------------------------------------------------- post-norm residual update
+// The residual stream of a post-norm block:  x <- (alpha x + d) * rsqrt(mean((alpha x + d)^2) + eps) * w,
+// written back in float32; `out` (may be null) receives the same row rounded to the
+// activation dtype, which is what the next sub-layer's products read.  The addend d comes as
+// one row of `delta` or as float32 slices, as for rmsnorm_kernel.  One block per row.
+template <typename TA, typename TW>
+__global__ void scaled_add_rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                                          DeltaParts dp, const TW* __restrict__ weight,
+                                          TA* __restrict__ out, int hidden, float alpha, float eps) {
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  float* res = residual + (size_t)r * hidden;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float d = 0.0f;
+    if (delta) {
+      d = to_f32<TA>(delta[(size_t)r * hidden + i]);
+    } else if (dp.n_parts > 0) {
+      for (int p = 0; p < dp.n_parts; ++p) d += dp.parts[(size_t)p * dp.stride + (size_t)r * hidden + i];
+      d = to_f32<TA>(from_f32<TA>(d));
+    }
+    const float y = fmaf(alpha, res[i], d);
+    srow[i] = y;
+    ss += y * y;
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float y = (srow[i] * rstd) * to_f32<TW>(weight[i]);
+    res[i] = y;
+    if (out) out[(size_t)r * hidden + i] = from_f32<TA>(y);
+  }
+}
+
+// out = residual (+ delta, which is then also added into residual) rounded to the activation dtype
+template <typename TA>
+__global__ void residual_cast_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                                     TA* __restrict__ out, long long total) {
+  pdl_wait();
+  pdl_trigger();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float x = residual[i];
+    if (delta) {
+      x += to_f32<TA>(delta[i]);
+      residual[i] = x;
+    }
+    out[i] = from_f32<TA>(x);
+  }
+}
+
+// ------------------------------------------------------------ squared ReLU
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, long long total) {
+  pdl_wait();
+  pdl_trigger();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float x = fmaxf(to_f32<T>(in[i]), 0.0f);
+    out[i] = from_f32<T>(x * x);
+  }
+}
+
 }  // namespace si
 
 SI_API int si_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
-                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+                           int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
   if (!table || !ids || !out || n_tokens < 0 || hidden <= 0 || vocab <= 0) return SI_ERR_ARG;
   if (n_tokens == 0) return SI_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == SI_F32)
     SI_LAUNCH(si::embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table,
-              ids, out, hidden, vocab);
+              ids, out, hidden, vocab, scale);
   else if (table_dtype == SI_BF16)
     SI_LAUNCH(si::embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
-              (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+              (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale);
   else
     return SI_ERR_DTYPE;
   return SI_OK;
@@ -305,5 +371,86 @@ SI_API int si_swiglu(const void* gu, void* out, int n_rows, int inter, int dtype
   } else {
     return SI_ERR_DTYPE;
   }
+  return SI_OK;
+}
+
+template <typename TA, typename TW>
+static int launch_scaled_add_rmsnorm(float* residual, const void* delta, si::DeltaParts dp,
+                                     const void* weight, void* out, int n_rows, int hidden,
+                                     float alpha, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return SI_ERR_TOO_LARGE;
+  auto kern = si::scaled_add_rmsnorm_kernel<TA, TW>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int threads = (hidden / 4 + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  if (threads < 64) threads = 64;
+  SI_LAUNCH(kern, n_rows, threads, smem, stream, residual, (const TA*)delta, dp, (const TW*)weight,
+            (TA*)out, hidden, alpha, eps);
+  return SI_OK;
+}
+
+// residual[r] <- rmsnorm(alpha * residual[r] + addend[r]) * weight, in float32 and in place;
+// out (optional) = the same rows in act_dtype.  The addend as for si_rmsnorm (delta, or float32
+// slices, or neither).
+SI_API int si_scaled_add_rmsnorm(float* residual, const void* delta, const float* parts, int n_parts,
+                                 long long part_stride, const void* weight, void* out, int n_rows,
+                                 int hidden, float alpha, float eps, int act_dtype, int weight_dtype,
+                                 cudaStream_t stream) {
+  if (!residual || !weight || n_rows < 0 || hidden <= 0 || !(eps > 0.0f)) return SI_ERR_ARG;
+  if (n_parts < 0 || (n_parts > 0 && (!parts || delta || part_stride < 0))) return SI_ERR_ARG;
+  if (n_rows == 0) return SI_OK;
+  si::DeltaParts dp;
+  dp.parts = n_parts > 0 ? parts : nullptr;
+  dp.n_parts = n_parts;
+  dp.stride = part_stride;
+  if (act_dtype == SI_F32 && weight_dtype == SI_F32)
+    return launch_scaled_add_rmsnorm<float, float>(residual, delta, dp, weight, out, n_rows, hidden, alpha, eps, stream);
+  if (act_dtype == SI_BF16 && weight_dtype == SI_F32)
+    return launch_scaled_add_rmsnorm<__nv_bfloat16, float>(residual, delta, dp, weight, out, n_rows, hidden, alpha, eps, stream);
+  if (act_dtype == SI_BF16 && weight_dtype == SI_BF16)
+    return launch_scaled_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(residual, delta, dp, weight, out, n_rows, hidden, alpha, eps, stream);
+  if (act_dtype == SI_F32 && weight_dtype == SI_BF16)
+    return launch_scaled_add_rmsnorm<float, __nv_bfloat16>(residual, delta, dp, weight, out, n_rows, hidden, alpha, eps, stream);
+  return SI_ERR_DTYPE;
+}
+
+static inline int elementwise_blocks(long long total, int threads) {
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+
+SI_API int si_residual_cast(float* residual, const void* delta, void* out, long long total, int dtype,
+                            cudaStream_t stream) {
+  if (!residual || !out || total < 0) return SI_ERR_ARG;
+  if (total == 0) return SI_OK;
+  const int threads = 256;
+  if (dtype == SI_BF16)
+    SI_LAUNCH(si::residual_cast_kernel<__nv_bfloat16>, elementwise_blocks(total, threads), threads, 0,
+              stream, residual, (const __nv_bfloat16*)delta, (__nv_bfloat16*)out, total);
+  else if (dtype == SI_F32)
+    SI_LAUNCH(si::residual_cast_kernel<float>, elementwise_blocks(total, threads), threads, 0, stream,
+              residual, (const float*)delta, (float*)out, total);
+  else
+    return SI_ERR_DTYPE;
+  return SI_OK;
+}
+
+SI_API int si_relu2(const void* in, void* out, long long total, int dtype, cudaStream_t stream) {
+  if (!in || !out || total < 0) return SI_ERR_ARG;
+  if (total == 0) return SI_OK;
+  const int threads = 256;
+  if (dtype == SI_BF16)
+    SI_LAUNCH(si::relu2_kernel<__nv_bfloat16>, elementwise_blocks(total, threads), threads, 0, stream,
+              (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total);
+  else if (dtype == SI_F32)
+    SI_LAUNCH(si::relu2_kernel<float>, elementwise_blocks(total, threads), threads, 0, stream,
+              (const float*)in, (float*)out, total);
+  else
+    return SI_ERR_DTYPE;
   return SI_OK;
 }

@@ -120,6 +120,9 @@ class StepContext:
     # output of the sub-layer now running takes ops.PartialSums (parts/base.py, Norm)
     partial_sums_ok: bool = False
     next_takes_partial_sums: bool = False
+    # (stream, rows): the float32 stream whose rows a block has left rounded to the activation
+    # dtype, valid while nothing has been added to the stream since (parts/block.py, postnorm)
+    stream_rounded: Any = None
 
 
 _FEW_ROWS = 8            # up to this many changed block-table rows are copied span by span,

@@ -10,7 +10,7 @@ import torch
 from ..config.model_config import ModelConfig
 from ..config.registry import architecture_of, read_config
 from ..parts.base import Runtime
-from ..weights.loader import load_tensors
+from ..weights.loader import load_tensors, tensor_shapes
 from ..weights.random_init import _STORE_DTYPES, random_tensors
 from .plan import DecoderModel
 
@@ -33,7 +33,7 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",
     """Read ``config.json``, pick the architecture from it, load and bind the weights."""
     rt = runtime_for(dtype, device)
     arch, cfg = read_config(model_dir)
-    model = DecoderModel(arch.plan(cfg))
+    model = DecoderModel(arch.plan_for(cfg, tensor_shapes(model_dir) if arch.reads_shapes else None))
     tensors = load_tensors(model_dir, model.tensor_specs(), model.optional_tensor_names(), rt)
     model.bind(tensors, rt)
     return cfg, model
@@ -45,7 +45,7 @@ def random_model(config: dict[str, Any], seed: int, dtype: str | torch.dtype = "
     rt = runtime_for(dtype, device)
     arch = architecture_of(config)
     cfg = arch.config_class.from_dict(config)
-    model = DecoderModel(arch.plan(cfg))
+    model = DecoderModel(arch.plan_for(cfg))
     store = _STORE_DTYPES[getattr(cfg, "torch_dtype", "bfloat16")]
     model.bind(random_tensors(model.tensor_specs(), seed, rt, store), rt)
     return cfg, model

@@ -176,9 +176,8 @@ class DecoderModel:
                 else self.final_norm
             ctx.next_takes_partial_sums = bool(taker is not None and taker.takes_partial_sums)
             cache = caches[step.cache_entry]
-            if cache is not None and cache.writes != step.writes_cache:
-                cache = LayerCache(cache.spec, cache.group, cache.pool, cache.state,
-                                   cache.page_size, step.writes_cache)
+            if cache is not None:
+                cache = cache.with_writes(step.writes_cache)
             delta = self.blocks[step.layer].forward(residual, delta, ctx, cache)
         if ctx.num_logit_rows == 0:
             return ctx.ws.get("logits", (0, self.plan.vocab_size), torch.float32,

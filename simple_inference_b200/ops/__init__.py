@@ -24,7 +24,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 _CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tc.cu", "gemm_tc2.cu",
-                 "attention_generic.cu", "sampling.cu"]
+                 "attention_generic.cu", "window_pool_attention.cu", "delta_rule.cu", "sampling.cu"]
 
 _ERRORS = {
     -1: "bad argument (null pointer, negative size or misaligned pointer)",
@@ -130,15 +130,16 @@ def _i32(t: torch.Tensor | None, name: str) -> None:
 
 # ----------------------------------------------------------------- row-wise
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out[t] = table[ids[t]]`` as float32 (the residual stream)."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
+                 scale: float = 1.0) -> torch.Tensor:
+    """``out[t] = scale * table[ids[t]]`` as float32 (the residual stream)."""
     _dev(table, ids, out)
     _i32(ids, "ids")
     n, hidden = out.shape
     if out.dtype != torch.float32 or table.shape[1] != hidden or ids.numel() < n:
         raise KernelError("embed_gather: shape or dtype mismatch")
     _check(core().si_embed_gather(_p(table), _dt(table), _p(ids), _p(out), n, hidden,
-                                  table.shape[0], _stream()), "embed_gather")
+                                  table.shape[0], _c_float(scale), _stream()), "embed_gather")
     return out
 
 
@@ -201,6 +202,56 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: shape or dtype mismatch")
     _check(core().si_swiglu(_p(gate_up), _p(out), n, inter, _dt(out), _stream()), "swiglu")
+    return out
+
+
+def scaled_add_rmsnorm(residual: torch.Tensor, weight: torch.Tensor, alpha: float, eps: float,
+                       out: torch.Tensor | None, delta: "torch.Tensor | PartialSums | None" = None) -> None:
+    """The residual update of a post-norm block, in float32 and in place:
+    ``residual <- norm(alpha * residual + delta) * weight``; ``out`` (optional) receives the new
+    rows rounded to the activation dtype.  ``delta`` may be the ``PartialSums`` of a product."""
+    parts = None
+    if isinstance(delta, PartialSums):
+        parts, delta = delta.slices, None
+    _dev(residual, weight, out, delta, parts)
+    n_rows, hidden = residual.shape
+    if residual.dtype != torch.float32 or weight.numel() != hidden:
+        raise KernelError("scaled_add_rmsnorm: residual must be float32, the gain of its width")
+    act = out if out is not None else delta
+    if out is not None and tuple(out.shape) != (n_rows, hidden):
+        raise KernelError("scaled_add_rmsnorm: out must have the shape of residual")
+    if delta is not None and (tuple(delta.shape) != (n_rows, hidden) or
+                              (out is not None and delta.dtype != out.dtype)):
+        raise KernelError("scaled_add_rmsnorm: delta must have the shape of residual and the dtype of out")
+    if parts is not None and (parts.dtype != torch.float32 or parts.dim() != 3 or
+                              tuple(parts.shape[1:]) != (n_rows, hidden)):
+        raise KernelError("scaled_add_rmsnorm: partial sums must be float32 [splits, rows, width]")
+    _check(core().si_scaled_add_rmsnorm(
+        _p(residual), _p(delta), _p(parts), 0 if parts is None else parts.shape[0],
+        ctypes.c_longlong(0 if parts is None else parts.stride(0)), _p(weight), _p(out), n_rows,
+        hidden, _c_float(alpha), _c_float(eps), _dt(act) if act is not None else 0, _dt(weight),
+        _stream()), "scaled_add_rmsnorm")
+
+
+def residual_cast(residual: torch.Tensor, out: torch.Tensor, delta: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = residual`` rounded to the activation dtype; with ``delta``, ``residual += delta``
+    first (in float32, in place)."""
+    _dev(residual, out, delta)
+    if residual.dtype != torch.float32 or out.shape != residual.shape or \
+            (delta is not None and (delta.shape != residual.shape or delta.dtype != out.dtype)):
+        raise KernelError("residual_cast: shapes or dtypes do not fit")
+    _check(core().si_residual_cast(_p(residual), _p(delta), _p(out),
+                                   ctypes.c_longlong(residual.numel()), _dt(out), _stream()),
+           "residual_cast")
+    return out
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = max(x, 0)^2`` in float32 arithmetic (``out`` may be ``x``)."""
+    _dev(x, out)
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("relu2: shape or dtype mismatch")
+    _check(core().si_relu2(_p(x), _p(out), ctypes.c_longlong(x.numel()), _dt(x), _stream()), "relu2")
     return out
 
 
@@ -567,6 +618,127 @@ def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, plan, group
         _p(ctx.cu_q), _p(ctx.positions), _p(plan.wide_seq), _p(plan.wide_start), plan.n_wide, _p(out),
         out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), int(window or 0),
         _stream()), "attn_prefill_tc")
+    return out
+
+
+# ------------------------------------- window attention with pooled blocks
+
+def window_pool_prepare(qkv: torch.Tensor, positions: torch.Tensor, q_gain: torch.Tensor,
+                        k_gain: torch.Tensor, freq_qk: torch.Tensor | None, amplitude: float,
+                        rot_dims: int, freq_v: torch.Tensor | None, slots: torch.Tensor | None,
+                        pool: torch.Tensor | None, num_q_heads: int, num_kv_heads: int, key_dim: int,
+                        value_dim: int, rows: int, eps: float, write_kv: bool) -> None:
+    """Queries and keys of a step's tokens: RMS norm over the whole projection, rotation of the
+    first ``rot_dims`` dimensions of each head; values turned over all their dimensions
+    (``freq_v``; None leaves them); queries stay in ``qkv`` (in place), keys and values go to
+    the token cache (planes layout, ``rows`` tokens a page) at ``slots``."""
+    _dev(qkv, positions, q_gain, k_gain, freq_qk, freq_v, slots, pool)
+    _i32(positions, "positions"); _i32(slots, "slots")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_q_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim:
+        raise KernelError("window_pool_prepare: qkv width does not fit the head counts and sizes")
+    if q_gain.numel() != num_q_heads * key_dim or k_gain.numel() != num_kv_heads * key_dim \
+            or q_gain.dtype != k_gain.dtype:
+        raise KernelError("window_pool_prepare: the gains cover the whole query and key projections")
+    for f, want, name in ((freq_qk, rot_dims // 2, "freq_qk"), (freq_v, value_dim // 2, "freq_v")):
+        if f is not None and (f.dtype != torch.float32 or f.numel() != want):
+            raise KernelError(f"window_pool_prepare: {name} must be float32 of {want} entries")
+    if write_kv and (pool is None or slots is None or pool.dtype != qkv.dtype or slots.numel() < n):
+        raise KernelError("window_pool_prepare: pool (in qkv's dtype) and slots needed")
+    _check(core().si_wp_prepare(
+        _p(qkv), qkv.stride(0), _p(positions), _p(q_gain), _p(k_gain), _dt(q_gain), _p(freq_qk),
+        _c_float(amplitude), rot_dims, _p(freq_v), _p(slots), _p(pool), n, num_q_heads, num_kv_heads,
+        key_dim, value_dim, rows, _c_float(eps), 1 if write_kv else 0, _dt(qkv), _stream()),
+        "window_pool_prepare")
+
+
+def window_pool_summarise(positions: torch.Tensor, tok_seq: torch.Tensor, tok_pool: torch.Tensor,
+                          tok_table: torch.Tensor, tok_rows: int, blk_pool: torch.Tensor,
+                          blk_table: torch.Tensor, blk_rows: int, n_tokens: int, num_kv_heads: int,
+                          key_dim: int, value_dim: int, pool_size: int) -> None:
+    """Every token of the step that ends a block of ``pool_size`` positions writes the block's
+    row: the means of the block's keys and of its values as the token cache holds them."""
+    _dev(positions, tok_seq, tok_pool, tok_table, blk_pool, blk_table)
+    _i32(positions, "positions"); _i32(tok_seq, "tok_seq")
+    _i32(tok_table, "tok_table"); _i32(blk_table, "blk_table")
+    if tok_pool.dtype != blk_pool.dtype:
+        raise KernelError("window_pool_summarise: the two caches must have one dtype")
+    _check(core().si_wp_pool(
+        _p(positions), _p(tok_seq), _p(tok_pool), _p(tok_table), tok_table.stride(0), tok_rows,
+        _p(blk_pool), _p(blk_table), blk_table.stride(0), blk_rows, n_tokens, num_kv_heads, key_dim,
+        value_dim, pool_size, _dt(tok_pool), _stream()), "window_pool_summarise")
+
+
+def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor,
+                          tok_pool: torch.Tensor, tok_table: torch.Tensor, tok_rows: int,
+                          blk_pool: torch.Tensor | None, blk_table: torch.Tensor | None,
+                          blk_rows: int, out: torch.Tensor, num_q_heads: int, num_kv_heads: int,
+                          key_dim: int, value_dim: int, scale: float, window: int | None,
+                          pool_size: int | None, freq_v: torch.Tensor | None) -> torch.Tensor:
+    """Attention of every token over the last ``window`` tokens of its request and the pooled
+    blocks wholly before them, one softmax over both, float32 arithmetic; each head's output is
+    turned back by the query's position (``freq_v``; None leaves it).  ``q`` may be the fused
+    projection buffer: its first ``num_q_heads * key_dim`` columns are read."""
+    _dev(positions, tok_seq, tok_pool, tok_table, blk_pool, blk_table, out, freq_v)
+    if not q.is_cuda or q.stride(1) != 1 or q.dtype != tok_pool.dtype or out.dtype != q.dtype:
+        raise KernelError("window_pool_attention: q, the cache and out must share a dtype; q rows contiguous")
+    _i32(positions, "positions"); _i32(tok_seq, "tok_seq")
+    _i32(tok_table, "tok_table"); _i32(blk_table, "blk_table")
+    n = out.shape[0]
+    if out.shape[1] != num_q_heads * value_dim:
+        raise KernelError("window_pool_attention: out holds a value head per query head")
+    _check(core().si_wp_attention(
+        _p(q), q.stride(0), _p(positions), _p(tok_seq), _p(tok_pool), _p(tok_table),
+        tok_table.stride(0), tok_rows, _p(blk_pool), _p(blk_table),
+        0 if blk_table is None else blk_table.stride(0), blk_rows, _p(out), out.stride(0), n,
+        num_q_heads, num_kv_heads, key_dim, value_dim, _c_float(scale), int(window or 0),
+        int(pool_size or 0), _p(freq_v), _dt(q), _stream()), "window_pool_attention")
+    return out
+
+
+# ------------------------------------------------------ generalised delta rule
+
+def delta_prepare(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+                  prep: torch.Tensor, num_heads: int, head_dim: int, rank: int) -> None:
+    """Per token, in float32: decay, unit key and rate times unit key of every head, from the
+    fused projection ``[r | k | v | g | a | low]`` (csrc/delta_rule.cu)."""
+    _dev(proj, w2, w0, a_bias, prep)
+    n, hd = proj.shape[0], num_heads * head_dim
+    if proj.shape[1] != 5 * hd + rank or tuple(w2.shape) != (hd, rank) or w2.dtype != proj.dtype:
+        raise KernelError("delta_prepare: projection or decay matrix does not fit")
+    if w0.dtype != torch.float32 or a_bias.dtype != torch.float32 or w0.numel() != hd or \
+            a_bias.numel() != hd or prep.dtype != torch.float32 or tuple(prep.shape) != (n, 3 * hd):
+        raise KernelError("delta_prepare: biases and output are float32 of the heads' width")
+    _check(core().si_delta_prepare(_p(proj), proj.stride(0), _p(w2), _p(w0), _p(a_bias), _p(prep), n,
+                                   num_heads, head_dim, rank, _dt(proj), _stream()), "delta_prepare")
+
+
+def delta_recurrence(proj: torch.Tensor, prep: torch.Tensor, cu_q: torch.Tensor,
+                     seq_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, n_seqs: int,
+                     num_heads: int, head_dim: int) -> None:
+    """The scan over each sequence's tokens of the step; ``state`` ``[slots, heads, D, D]``
+    float32 is read at the sequence's slot and written back; ``out`` ``[tokens, heads*D]`` float32."""
+    _dev(proj, prep, cu_q, seq_slots, state, out)
+    _i32(cu_q, "cu_q"); _i32(seq_slots, "seq_slots")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (num_heads, head_dim, head_dim) \
+            or out.dtype != torch.float32 or out.shape[1] != num_heads * head_dim:
+        raise KernelError("delta_recurrence: state or output does not fit")
+    _check(core().si_delta_recurrence(_p(proj), proj.stride(0), _p(prep), _p(cu_q), _p(seq_slots),
+                                      _p(state), _p(out), n_seqs, num_heads, head_dim, _dt(proj),
+                                      _stream()), "delta_recurrence")
+
+
+def delta_output(o: torch.Tensor, proj: torch.Tensor, gain: torch.Tensor, out: torch.Tensor,
+                 num_heads: int, head_dim: int, eps: float) -> torch.Tensor:
+    """``out = o / rms_head(o) * gain * sigmoid(g)`` with g the fourth block of ``proj``."""
+    _dev(o, proj, gain, out)
+    n = o.shape[0]
+    if o.dtype != torch.float32 or tuple(out.shape) != (n, num_heads * head_dim) or \
+            out.dtype != proj.dtype or gain.numel() != num_heads * head_dim:
+        raise KernelError("delta_output: shapes or dtypes do not fit")
+    _check(core().si_delta_output(_p(o), _p(proj), proj.stride(0), _p(gain), _p(out), n, num_heads,
+                                  head_dim, _c_float(eps), _dt(proj), _dt(gain), _stream()),
+           "delta_output")
     return out
 
 

@@ -7,7 +7,7 @@ from .base import (Block, CacheSpec, Embedding, FeedForward, Head, LayerCache, M
 from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                        UnknownPartError, register_block, register_embedding, register_feed_forward,
                        register_head, register_mixer, register_norm, register_position_encoding)
-from . import norm, rope, attention, mlp, embedding, block  # noqa: F401  (register the built-in kinds)
+from . import norm, rope, attention, pooled_attention, delta, mlp, embedding, block  # noqa: F401  (register the built-in kinds)
 
 __all__ = [
     "Block", "CacheSpec", "Embedding", "FeedForward", "Head", "LayerCache", "Mixer", "Norm",

@@ -85,13 +85,62 @@ class StateSpec:
         return tuple(self.shape)
 
 
+@dataclass(frozen=True)
+class KeyValuePlanesSpec:
+    """Keys and values of different widths, kept in pages as two planes.
+
+    A page of ``page_size`` tokens has ``rows = page_size // tokens_per_row`` rows: first the
+    keys ``[kv_heads, rows, key_dim]``, then the values ``[kv_heads, rows, value_dim]``, flat.
+    ``tokens_per_row`` 1 is a row per token; ``tokens_per_row`` P is a row per block of P
+    tokens (a summary of the block), so that such a cache grows by a row every P tokens and
+    its own ``page_size`` must be a multiple of P.  ``window``: how many of the newest tokens
+    a later step can still ask for (None: all); pages wholly before them are given back.
+    """
+
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: int | None = None
+    page_size: int | None = None
+    tokens_per_row: int = 1
+
+    storage = "pages"
+
+    def rows(self, page_size: int) -> int:
+        if page_size % self.tokens_per_row != 0:
+            raise ValueError(f"a page of {page_size} tokens does not hold whole rows of "
+                             f"{self.tokens_per_row} tokens")
+        return page_size // self.tokens_per_row
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (self.num_kv_heads * self.rows(page_size) * (self.key_dim + self.value_dim),)
+
+
+@dataclass(frozen=True)
+class CompositeSpec:
+    """Several kinds of memory kept by one mixer (say, recent tokens in a window and a
+    summary of older ones): each member is stored as its own spec says, and the mixer finds
+    them, in this order, in ``LayerCache.members``."""
+
+    members: tuple
+
+    storage = "composite"
+
+
+def spec_members(spec) -> tuple:
+    """The specs a cache entry is made of: the spec itself, or a composite's members."""
+    if spec is None:
+        return ()
+    return tuple(spec.members) if getattr(spec, "storage", None) == "composite" else (spec,)
+
+
 # What a mixer may return from ``cache_spec()``.  The cache manager knows two ways of
 # storing: ``storage == "pages"`` (memory that grows with the request: the spec says how one
 # page of ``page_size`` tokens is shaped, ``page_shape(page_size)``, which page size it wants,
 # ``page_size`` or None, and whether old pages may go, ``window``) and ``storage == "slots"``
 # (one row of ``slot_shape()`` per request).  Specs that compare equal share a group of pages.
 # Any frozen dataclass with these attributes will do; the two above are the built-in ones.
-CacheSpec = PagedKVSpec | StateSpec
+CacheSpec = PagedKVSpec | StateSpec | KeyValuePlanesSpec | CompositeSpec
 
 
 @dataclass
@@ -104,6 +153,7 @@ class LayerCache:
     layer group's block tables and write slots in the ``StepContext``.  For a spec
     stored in slots: ``state`` is ``[slots+1, *spec.slot_shape()]``, row = the
     request's slot, the last row is scratch.
+    For a ``CompositeSpec``: ``members`` holds one ``LayerCache`` per member spec.
     ``writes`` is False when the layer only reads a cache that another layer
     filled.
     """
@@ -114,6 +164,15 @@ class LayerCache:
     state: torch.Tensor | None = None
     page_size: int = 0
     writes: bool = True
+    members: "list[LayerCache] | None" = None
+
+    def with_writes(self, writes: bool) -> "LayerCache":
+        """The same view for a run that writes (or only reads) the entry."""
+        if writes == self.writes:
+            return self
+        members = None if self.members is None else [m.with_writes(writes) for m in self.members]
+        return LayerCache(self.spec, self.group, self.pool, self.state, self.page_size, writes,
+                          members)
 
 
 @dataclass

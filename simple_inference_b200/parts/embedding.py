@@ -20,9 +20,13 @@ from .registry import register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    """``x0[t] = scale * E[id[t]]`` (``scale`` 1 for Llama); the product is formed in float32.
+    A tied head multiplies by ``E`` itself, without the scale."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
+        self.scale = float(scale)
         self.weight: torch.Tensor | None = None
 
     def tensors(self) -> dict[str, TensorSpec]:
@@ -35,7 +39,7 @@ class TokenEmbedding(Embedding):
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         n = token_ids.shape[0]
         residual = ctx.ws.get("residual", (n, self.hidden_size), torch.float32)
-        ops.embed_gather(self.weight, token_ids, residual)
+        ops.embed_gather(self.weight, token_ids, residual, self.scale)
         return residual
 
     def output_matrix(self) -> torch.Tensor:

@@ -48,3 +48,34 @@ class SwiGLU(FeedForward):
             ops.swiglu(gate_up, hidden)
         return ops.linear_for_residual(hidden, self.w_down, ctx.ws, "mlp.down",
                                        getattr(ctx, "partial_sums_ok", False))
+
+
+@register_feed_forward("relu2")
+class SquaredReLU(FeedForward):
+    """``y = W_down relu(W_up x)^2``: two matrices, the square of the rectifier between them
+    (float32 arithmetic, one rounding)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.w_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {
+            "w_up": TensorSpec((self.intermediate_size, self.hidden_size)),
+            "w_down": TensorSpec((self.hidden_size, self.intermediate_size)),
+        }
+
+    def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().bind(tensors, rt)
+        self.w_up = tensors["w_up"]
+        self.w_down = tensors["w_down"]
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        n = x.shape[0]
+        hidden = ctx.ws.get("mlp.hidden", (n, self.intermediate_size), x.dtype)
+        ops.linear(x, self.w_up, hidden)
+        ops.relu2(hidden, hidden)
+        return ops.linear_for_residual(hidden, self.w_down, ctx.ws, "mlp.down",
+                                       getattr(ctx, "partial_sums_ok", False))

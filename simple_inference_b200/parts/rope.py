@@ -51,6 +51,37 @@ def rope_inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) 
     return torch.tensor(scaled, dtype=torch.float32)
 
 
+def yarn_frequencies(dims: int, base: float, scaling: dict | None) -> tuple[torch.Tensor, float]:
+    """float32 ``[dims/2]`` rotation frequencies with YaRN scaling, and the amplitude that
+    multiplies every cos and sin.
+
+    Plain: ``f_i = base^(-2i/dims)``, amplitude 1.  ``scaling`` = {factor s, original length
+    L, fast, slow}: a wave that makes t turns over L sits at dimension
+    ``d(t) = dims ln(L / (2 pi t)) / (2 ln base)``; between ``lo = max(floor d(fast), 0)`` and
+    ``hi = min(ceil d(slow), dims - 1)`` a ramp ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``
+    blends ``f_i`` (r = 0, fast waves) into ``f_i / s`` (r = 1, slow waves); the amplitude is
+    ``0.1 ln s + 1``.  Double precision per frequency, stored as float32.
+    """
+    half = dims // 2
+    freqs = [float(base) ** (-2.0 * i / dims) for i in range(half)]
+    amplitude = 1.0
+    if scaling:
+        s, length = float(scaling["factor"]), float(scaling["original"])
+
+        def dimension_of(turns: float) -> float:
+            return dims * math.log(length / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+        lo = max(math.floor(dimension_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(dimension_of(float(scaling["slow"]))), dims - 1)
+        span = max(hi - lo, 0.001)
+        for i in range(half):
+            ramp = min(max((i - lo) / span, 0.0), 1.0)
+            freqs[i] = freqs[i] / s * ramp + freqs[i] * (1.0 - ramp)
+        amplitude = 0.1 * math.log(s) + 1.0
+    return torch.tensor(freqs, dtype=torch.float64).to(torch.float32), amplitude
+
+
+
 @register_position_encoding("rope")
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, scaling: dict | None = None):

@@ -31,7 +31,7 @@ from .engine.runner import ModelRunner
 from .models.load import load_model
 
 PAGE_SIZE = 16          # tokens per page; request lengths are rounded up to 64, a multiple of it
-MAX_LIVE_REQUESTS = 8   # the protocol promises at most four at a time
+MAX_LIVE_REQUESTS = 4   # state slots; the protocol promises that no more requests are live at a time
 STEP_TOKEN_CAP = 4096   # a step that brings more tokens runs as several batches
 
 
@@ -80,7 +80,14 @@ def main(argv: list[str] | None = None) -> int:
     num_pages = max(1, (args.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE)
     max_seq_len = min(model.plan.max_positions, num_pages * PAGE_SIZE)
     cap = min(STEP_TOKEN_CAP, max_seq_len * MAX_LIVE_REQUESTS)
-    cache = CacheManager(model.cache_specs(), PAGE_SIZE, num_pages, MAX_LIVE_REQUESTS, cap,
+
+    def pages_of(page_size: int) -> int:
+        """Pages of a group for ``--max-tokens`` tokens; a group whose pages are longer than the
+        64 tokens that request lengths are rounded to may leave one page per request half used."""
+        n = max(1, (args.max_tokens + page_size - 1) // page_size)
+        return n if 64 % page_size == 0 else n + MAX_LIVE_REQUESTS
+
+    cache = CacheManager(model.cache_specs(), PAGE_SIZE, pages_of, MAX_LIVE_REQUESTS, cap,
                          dtype=rt.dtype, device=rt.device)
     runner = ModelRunner(model, cache, rt, cap, MAX_LIVE_REQUESTS, max_seq_len,
                          cuda_graphs=(args.dtype == "bfloat16"), max_logit_rows=cap)

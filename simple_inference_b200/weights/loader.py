@@ -62,6 +62,19 @@ def _shard_map(model_dir: Path) -> dict[str, Path]:
         return {name: single for name in f.keys()}
 
 
+def tensor_shapes(model_dir: str | Path) -> dict[str, tuple[int, ...]]:
+    """Name -> shape of every tensor the folder's safetensors files hold (headers only)."""
+    out: dict[str, tuple[int, ...]] = {}
+    by_file: dict[Path, list[str]] = {}
+    for name, path in _shard_map(Path(model_dir)).items():
+        by_file.setdefault(path, []).append(name)
+    for path, names in by_file.items():
+        with safe_open(str(path), framework="pt", device="cpu") as f:
+            for name in names:
+                out[name] = tuple(f.get_slice(name).get_shape())
+    return out
+
+
 def target_dtype(spec: TensorSpec, stored: torch.dtype, rt: Runtime) -> torch.dtype:
     if spec.kind == "table":
         return torch.int32

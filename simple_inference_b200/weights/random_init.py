@@ -52,7 +52,7 @@ def model_for_config(config: dict[str, Any]):
     from ..models.plan import DecoderModel
     arch = architecture_of(config)
     cfg = arch.config_class.from_dict(config)
-    return cfg, DecoderModel(arch.plan(cfg))
+    return cfg, DecoderModel(arch.plan_for(cfg))
 
 
 def write_random_model(folder: str | Path, config: dict[str, Any], seed: int,
