@@ -167,6 +167,7 @@ class DecoderModel:
         ``caches[e]`` is the view of cache entry ``e``.
         """
         residual = self.embedding.forward(ctx.token_ids, ctx)
+        ctx.stream_rounded = None   # a context may be run again (graph capture): nothing is rounded yet
         delta = None
         order = self.plan.run_order
         for i, step in enumerate(order):
