@@ -27,7 +27,8 @@ class Trace:
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, cwd=str(ROOT),
             env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
         self.n = 0
-        self.vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+        cfg = json.loads((Path(model_dir) / "config.json").read_text())
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
 
     def step(self, entries, end=()) -> torch.Tensor | None:
         """entries: [(id, tokens, want)].  Returns the logits written for this step, if any."""

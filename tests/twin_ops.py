@@ -19,8 +19,8 @@ import torch
 from tests import plain_llama
 
 
-def embed_gather(table, ids, out):
-    out.copy_(table[ids[: out.shape[0]].long()].float())
+def embed_gather(table, ids, out, scale=1.0):
+    out.copy_(table[ids[: out.shape[0]].long()].float() * scale)
     return out
 
 
