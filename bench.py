@@ -105,7 +105,7 @@ def fill_context(cache, runner, batch, vocab, seed):
     torch.cuda.synchronize()
 
 
-def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
+def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False, compare_eager=True):
     """Device-timed decode: per step one metadata copy, the captured graph, the sampling kernel."""
     import torch
     from simple_inference_b200 import ops
@@ -147,7 +147,8 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
     ms = start.elapsed_time(end) / steps
     launches = (ops.launch_count - k0) + (runner.replayed_kernels - r0)
     ctx_mean = DECODE_CONTEXT + 1 + warmup + (steps - 1) / 2
-    check = check_against_eager(runner, cache, batch, feed[0]) if not EAGER else None
+    # (running a step twice would advance a mixer's state twice: models with one skip the comparison)
+    check = check_against_eager(runner, cache, batch, feed[0]) if not EAGER and compare_eager else None
     del runner, cache
     torch.cuda.empty_cache()
     return ms, launches, ctx_mean, (clocks.summary() if clocks else None), check
@@ -469,6 +470,71 @@ def workload_8b_long_context(pk):
     return out
 
 
+# ---------------------------------------------------------------------------
+# --only sapanex: the Sapanex design beside Llama at equal layer sizes
+# ---------------------------------------------------------------------------
+SAPANEX_SHAPES = {
+    # name: (width, heads, kv_heads, head size, feed-forward width)
+    "1b": (2048, 32, 8, 64, 8192),
+    "3b": (3072, 24, 8, 128, 8192),
+}
+SAPANEX_WINDOW, SAPANEX_POOL, SAPANEX_LAYERS, SAPANEX_VOCAB = 1024, 16, 8, 32000
+
+
+def sapanex_config(shape: str) -> dict:
+    """Eight layers, one attention layer (window of 1,024 tokens, blocks of 16) before every
+    three delta-rule layers, each with a feed-forward, at the widths of the Llama shape."""
+    width, heads, kv_heads, dim, ff = SAPANEX_SHAPES[shape]
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "dim": dim, "heads": heads, "kv_heads": kv_heads, "vdim": dim, "scale": dim ** -0.5,
+        "mask": {"size": SAPANEX_WINDOW, "pool": SAPANEX_POOL},
+        "rot": {"base": 500000.0, "dims": dim // 2,
+                "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    delta = {"type": "general_delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"dim": dim, "heads": heads, "decay_rank": 64}}
+    layers = [attention if i % 4 == 0 else delta for i in range(SAPANEX_LAYERS)]
+    return {"architecture": "Sapanex", "embedding": {"scale": 1.0}, "layers": layers,
+            "norm": {"eps": 1e-5}, "postln_alpha": 1.0, "vocab": SAPANEX_VOCAB, "width": width}
+
+
+def llama_like(shape: str) -> dict:
+    width, heads, kv_heads, dim, ff = SAPANEX_SHAPES[shape]
+    return dict(LLAMA_3_2_3B, num_hidden_layers=SAPANEX_LAYERS, hidden_size=width,
+                num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=dim,
+                intermediate_size=ff, vocab_size=SAPANEX_VOCAB)
+
+
+def run_sapanex(args) -> int:
+    """Prefill of PREFILL_TOKENS tokens and decode at context DECODE_CONTEXT of the Sapanex
+    design and of Llama with the same width, heads, feed-forward width and number of layers
+    (random weights, bfloat16, device-timed)."""
+    import torch
+    from simple_inference_b200.models.load import random_model
+    out = {"only": "sapanex", "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT,
+           "layers": SAPANEX_LAYERS, "window": SAPANEX_WINDOW, "pool": SAPANEX_POOL, "shapes": {}}
+    shapes = [args.shape] if args.shape in SAPANEX_SHAPES and args.shape_given else list(SAPANEX_SHAPES)
+    for shape in shapes:
+        row = {}
+        for name, config in (("sapanex", sapanex_config(shape)), ("llama", llama_like(shape))):
+            cfg, model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+            pre_ms = time_prefill(model, cfg, reps=3)
+            entry = {"prefill_ms": round(pre_ms, 3),
+                     "prefill_tok_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1)}
+            for batch in (1, args.batch):
+                ms, launches, _, _, _ = time_decode(model, cfg, batch, args.steps, max(args.warmup, 3),
+                                                    compare_eager=False)
+                entry[f"decode_b{batch}_ms"] = round(ms, 4)
+                entry[f"decode_b{batch}_tok_s"] = round(batch / (ms * 1e-3), 1)
+                entry[f"decode_b{batch}_launches_per_step"] = launches // max(args.steps, 1)
+            row[name] = entry
+            del model
+            torch.cuda.empty_cache()
+        out["shapes"][shape] = row
+    print(json.dumps(out))
+    return 0
+
+
+
 def run_reference(args) -> int:
     """Run ``baseline/reference_arm.py`` in a process of its own (so that nothing of this
     package is imported beside the reference) and pass its JSON line on."""
@@ -506,19 +572,21 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 1B continuous-batching and 8B long-context workloads")
-    ap.add_argument("--only", choices=["decode", "prefill", "products"],
+    ap.add_argument("--only", choices=["decode", "prefill", "products", "sapanex"],
                     help="run one part and print a short record (for profiling; not the contract line)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for kernel-level profiles)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: the kernels of one replayed step with their real start "
                          "times (kineto), as text")
-    ap.add_argument("--shape", choices=["3b", "1b", "8b"], default="3b",
+    ap.add_argument("--shape", choices=["3b", "1b", "8b"], default=None,
                     help="with --only: the layer sizes (Llama 3.2 3B, 3.2 1B or 3.1 8B)")
     ap.add_argument("--context", type=int, default=None,
                     help="with --only decode: tokens each request holds (default 2048)")
     ap.add_argument("--prefill-tokens", type=int, default=None,
                     help="with --only prefill: length of the prompt (default 2048)")
     args = ap.parse_args()
+    args.shape_given = args.shape is not None
+    args.shape = args.shape or "3b"
     global EAGER, DECODE_CONTEXT, PREFILL_TOKENS, MAX_CONTEXT
     EAGER = args.eager
     if args.only and (args.context or args.prefill_tokens):   # other sizes than the headline's
@@ -542,6 +610,8 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device")
         return 1
+    if args.only == "sapanex":
+        return run_sapanex(args)
     pk, pk_src = peaks()
     config = dict(LLAMA_3_2_3B)
     if args.only and args.shape != "3b":

@@ -10,9 +10,10 @@
 // The projections r, k, v, g, a, low arrive as columns of one matrix product (activation
 // dtype); everything after them is float32: decays, rates, the unit key, the state, the
 // head-wise norm and the gate.  Three kernels:
-//   prepare     per token, in parallel: decay, u, rate*u as float32
+//   prepare     per token, in parallel: decay, u, rate*u, and k, r, v widened, as float32
 //   recurrence  per (sequence, head, slice of value channels): the scan over the step's
-//               tokens; the state comes from and returns to the request's slot
+//               tokens; the state comes from and returns to the request's slot; the tokens'
+//               inputs stream through a ring of shared-memory stages filled by cp.async
 //   output      per token, in parallel: head-wise norm, gain, gate
 // The scan's order is the token order, so a sequence's result is the same however its tokens
 // were cut into steps and whatever else the batch holds.
@@ -22,10 +23,14 @@ namespace si {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+constexpr int DELTA_PLANES = 6;   // prep[t][plane][heads*D]: decay, u, rate*u, k, r, v
+
 // proj columns: [r | k | v | g | a | low], each of the first five HD = heads*D wide, low L wide.
+// w2t is the decay's second matrix transposed, [L, HD], so that neighbouring channels read
+// neighbouring words.
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride,
-                                     const T* __restrict__ w2, const float* __restrict__ w0,
+                                     const T* __restrict__ w2t, const float* __restrict__ w0,
                                      const float* __restrict__ a_bias, float* __restrict__ prep,
                                      int heads, int D, int L) {
   extern __shared__ float low_s[];  // [L] tanh of the inner projection
@@ -45,33 +50,49 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride
   const float ss = block_sum(k * k, red);  // also orders low_s
   if (!mine) return;
   float z = z0;
-  const T* w2row = w2 + (size_t)col * L;
-  for (int l = 0; l < L; ++l) z = fmaf(to_f32<T>(w2row[l]), low_s[l], z);
+  for (int l = 0; l < L; ++l) z = fmaf(to_f32<T>(w2t[(size_t)l * HD + col]), low_s[l], z);
   const float decay = expf(-0.60653065971263342f * sigmoidf_(z));
   const float u = k / sqrtf(ss + 1e-6f);
   const float rate = sigmoidf_(to_f32<T>(row[4 * HD + col]) + bias);
-  float* dst = prep + (size_t)t * 3 * HD + col;
+  float* dst = prep + (size_t)t * DELTA_PLANES * HD + col;
   dst[0] = decay;
   dst[HD] = u;
   dst[2 * HD] = rate * u;
+  dst[3 * HD] = k;
+  dst[4 * HD] = to_f32<T>(row[col]);
+  dst[5 * HD] = to_f32<T>(row[2 * HD + col]);
 }
 
 // Threads of a block: DC value channels x KS lanes; lane ks of channel d keeps S[c][d] for
 // c = ks + KS*i, i < R, in registers (c >= D padded with zeros).  Tokens are taken in groups
-// of TB whose inputs are staged in shared memory.
+// of TB; a group's inputs ([TB][5][Dp] key-side planes and [TB][DC] values) are one stage of a
+// ring of NS stages that cp.async fills NS-1 groups ahead of the arithmetic.
 constexpr int DELTA_KS = 4;    // lanes that share one value channel
 constexpr int DELTA_DC = 32;   // value channels per block
-constexpr int DELTA_TB = 8;    // tokens staged at a time
+constexpr int DELTA_TB = 8;    // tokens per stage
+constexpr int DELTA_NS = 4;    // stages
 
-template <typename T, int R>
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int R, bool VEC>
 __global__ void __launch_bounds__(DELTA_KS * DELTA_DC)
-delta_recurrence_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ prep,
-                        const int* __restrict__ cu_q, const int* __restrict__ seq_slots,
-                        float* __restrict__ state, float* __restrict__ o_out, int heads, int D) {
-  extern __shared__ float sm[];
-  const int Dp = R * DELTA_KS;                 // padded number of key channels
-  float* in_s = sm;                            // [TB][5][Dp]: decay, u, rate*u, k, r
-  float* v_s = sm + DELTA_TB * 5 * Dp;         // [TB][DC]
+delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ cu_q,
+                        const int* __restrict__ seq_slots, float* __restrict__ state,
+                        float* __restrict__ o_out, int heads, int D) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int Dp = R * DELTA_KS;                      // padded number of key channels
+  constexpr int STAGE = DELTA_TB * (5 * Dp + DELTA_DC);  // floats per stage
   const int s = blockIdx.x, h = blockIdx.y;
   const int d0 = blockIdx.z * DELTA_DC;
   const int tid = threadIdx.x;
@@ -79,8 +100,12 @@ delta_recurrence_kernel(const T* __restrict__ proj, int proj_stride, const float
   const int d = d0 + dl;
   const bool col_ok = d < D;
   const int HD = heads * D;
-  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
-  const int slot = seq_slots[s];
+  const int dc = min(DELTA_DC, D - d0);                  // value channels of this block
+  const int t_begin = cu_q[s], t_end = cu_q[s + 1];     // the step's description: on the device
+  const int slot = seq_slots[s];                        // before the step's first kernel
+  // channels past D (and value channels past the head's) stay zero in every stage
+  for (int i = tid; i < DELTA_NS * STAGE; i += blockDim.x) sm[i] = 0.0f;
+  __syncthreads();
   pdl_wait();
   pdl_trigger();
   float* S_g = state + ((size_t)slot * heads + h) * D * D;
@@ -90,29 +115,54 @@ delta_recurrence_kernel(const T* __restrict__ proj, int proj_stride, const float
     const int c = ks + DELTA_KS * i;
     S[i] = (col_ok && c < D) ? S_g[(size_t)c * D + d] : 0.0f;
   }
-  for (int tb = t_begin; tb < t_end; tb += DELTA_TB) {
-    const int nt = min(DELTA_TB, t_end - tb);
-    __syncthreads();  // the previous group's inputs are no longer read
-    for (int idx = tid; idx < nt * 5 * Dp; idx += blockDim.x) {
-      const int c = idx % Dp, which = (idx / Dp) % 5, tt = idx / (5 * Dp);
-      const size_t t = (size_t)(tb + tt);
-      float x = 0.0f;
-      if (c < D) {
-        if (which < 3) x = prep[t * 3 * HD + (size_t)which * HD + h * D + c];
-        else if (which == 3) x = to_f32<T>(proj[t * proj_stride + HD + h * D + c]);
-        else x = to_f32<T>(proj[t * proj_stride + h * D + c]);
+  const int n_groups = (t_end - t_begin + DELTA_TB - 1) / DELTA_TB;
+  auto fetch = [&](int g) {   // group g of the sequence into stage g % NS
+    if (g < n_groups) {
+      float* st = sm + (g % DELTA_NS) * STAGE;
+      const int tb = t_begin + g * DELTA_TB;
+      const int nt = min(DELTA_TB, t_end - tb);
+      if (VEC) {   // D is a multiple of 4: every run below starts on a 16-byte boundary
+        const int per_plane = D / 4, per_tok = 5 * per_plane + (dc + 3) / 4;
+        for (int idx = tid; idx < nt * per_tok; idx += blockDim.x) {
+          const int tt = idx / per_tok, e = idx - tt * per_tok;
+          const float* src = prep + (size_t)(tb + tt) * DELTA_PLANES * HD + h * D;
+          if (e < 5 * per_plane) {
+            const int which = e / per_plane, c4 = (e - which * per_plane) * 4;
+            cp_async16(st + (tt * 5 + which) * Dp + c4, src + (size_t)which * HD + c4);
+          } else {
+            const int c4 = (e - 5 * per_plane) * 4;
+            cp_async16(st + DELTA_TB * 5 * Dp + tt * DELTA_DC + c4, src + (size_t)5 * HD + d0 + c4);
+          }
+        }
+      } else {
+        const int per_tok = 5 * D + dc;
+        for (int idx = tid; idx < nt * per_tok; idx += blockDim.x) {
+          const int tt = idx / per_tok, e = idx - tt * per_tok;
+          const float* src = prep + (size_t)(tb + tt) * DELTA_PLANES * HD + h * D;
+          if (e < 5 * D) {
+            const int which = e / D, c = e - which * D;
+            cp_async4(st + (tt * 5 + which) * Dp + c, src + (size_t)which * HD + c);
+          } else {
+            const int c = e - 5 * D;
+            cp_async4(st + DELTA_TB * 5 * Dp + tt * DELTA_DC + c, src + (size_t)5 * HD + d0 + c);
+          }
+        }
       }
-      in_s[idx] = x;
     }
-    for (int idx = tid; idx < nt * DELTA_DC; idx += blockDim.x) {
-      const int dd = idx % DELTA_DC, tt = idx / DELTA_DC;
-      v_s[idx] = (d0 + dd < D)
-                     ? to_f32<T>(proj[(size_t)(tb + tt) * proj_stride + 2 * HD + h * D + d0 + dd])
-                     : 0.0f;
-    }
-    __syncthreads();
+    cp_async_commit();   // an empty group keeps the count uniform
+  };
+#pragma unroll
+  for (int g = 0; g < DELTA_NS - 1; ++g) fetch(g);
+  for (int g = 0; g < n_groups; ++g) {
+    fetch(g + DELTA_NS - 1);          // into the stage that group g-1 has left
+    cp_async_wait<DELTA_NS - 1>();    // this thread's copies of group g have landed
+    __syncthreads();                  // and everyone else's
+    const float* st = sm + (g % DELTA_NS) * STAGE;
+    const float* v_s = st + DELTA_TB * 5 * Dp;
+    const int tb = t_begin + g * DELTA_TB;
+    const int nt = min(DELTA_TB, t_end - tb);
     for (int tt = 0; tt < nt; ++tt) {
-      const float* w_s = in_s + tt * 5 * Dp;
+      const float* w_s = st + tt * 5 * Dp;
       const float* u_s = w_s + Dp;
       const float* au_s = w_s + 2 * Dp;
       const float* k_s = w_s + 3 * Dp;
@@ -140,7 +190,9 @@ delta_recurrence_kernel(const T* __restrict__ proj, int proj_stride, const float
       for (int off = DELTA_KS / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (ks == 0 && col_ok) o_out[(size_t)(tb + tt) * HD + h * D + d] = o;
     }
+    __syncthreads();   // the stage may be refilled
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int c = ks + DELTA_KS * i;
@@ -169,10 +221,10 @@ __global__ void delta_output_kernel(const float* __restrict__ o, const T* __rest
 
 }  // namespace si
 
-SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2, const float* w0,
+SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2t, const float* w0,
                             const float* a_bias, float* prep, int n_tokens, int heads, int D, int L,
                             int dtype, cudaStream_t stream) {
-  if (!proj || !w2 || !w0 || !a_bias || !prep || n_tokens < 0 || heads <= 0 || D <= 0 || L <= 0)
+  if (!proj || !w2t || !w0 || !a_bias || !prep || n_tokens < 0 || heads <= 0 || D <= 0 || L <= 0)
     return SI_ERR_ARG;
   if (D > 1024 || heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_tokens == 0) return SI_OK;
@@ -182,38 +234,47 @@ SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2, c
   if (smem > 48 * 1024) return SI_ERR_TOO_LARGE;
   if (dtype == SI_BF16)
     SI_LAUNCH(si::delta_prepare_kernel<__nv_bfloat16>, grid, threads, smem, stream,
-              (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)w2, w0, a_bias, prep,
+              (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)w2t, w0, a_bias, prep,
               heads, D, L);
   else if (dtype == SI_F32)
     SI_LAUNCH(si::delta_prepare_kernel<float>, grid, threads, smem, stream, (const float*)proj,
-              proj_stride, (const float*)w2, w0, a_bias, prep, heads, D, L);
+              proj_stride, (const float*)w2t, w0, a_bias, prep, heads, D, L);
   else
     return SI_ERR_DTYPE;
   return SI_OK;
 }
 
-template <typename T, int R>
-static int launch_delta_recurrence(const void* proj, int proj_stride, const float* prep,
-                                   const int* cu_q, const int* seq_slots, float* state, float* o_out,
-                                   int n_seqs, int heads, int D, cudaStream_t stream) {
-  const size_t smem = (size_t)si::DELTA_TB * (5 * R * si::DELTA_KS + si::DELTA_DC) * sizeof(float);
-  auto kern = si::delta_recurrence_kernel<T, R>;
+template <int R, bool VEC>
+static int launch_delta_recurrence(const float* prep, const int* cu_q, const int* seq_slots,
+                                   float* state, float* o_out, int n_seqs, int heads, int D,
+                                   cudaStream_t stream) {
+  const size_t smem = (size_t)si::DELTA_NS * si::DELTA_TB * (5 * R * si::DELTA_KS + si::DELTA_DC) *
+                      sizeof(float);
+  auto kern = si::delta_recurrence_kernel<R, VEC>;
   if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
   dim3 grid(n_seqs, heads, (D + si::DELTA_DC - 1) / si::DELTA_DC);
-  SI_LAUNCH(kern, grid, si::DELTA_KS * si::DELTA_DC, smem, stream, (const T*)proj, proj_stride, prep,
-            cu_q, seq_slots, state, o_out, heads, D);
+  SI_LAUNCH(kern, grid, si::DELTA_KS * si::DELTA_DC, smem, stream, prep, cu_q, seq_slots, state,
+            o_out, heads, D);
   return SI_OK;
 }
 
-template <typename T>
-static int delta_recurrence_by_size(const void* proj, int proj_stride, const float* prep,
-                                    const int* cu_q, const int* seq_slots, float* state, float* o_out,
-                                    int n_seqs, int heads, int D, cudaStream_t stream) {
+// state: [slots, heads, D, D] float32 (key channel, value channel); sequence s of the step owns
+// the tokens cu_q[s]..cu_q[s+1]-1 and the slot seq_slots[s].  prep: what si_delta_prepare
+// wrote.  o_out: [n_tokens, heads*D] float32.
+SI_API int si_delta_recurrence(const float* prep, const int* cu_q, const int* seq_slots,
+                               float* state, float* o_out, int n_seqs, int heads, int D,
+                               cudaStream_t stream) {
+  if (!prep || !cu_q || !seq_slots || !state || !o_out || n_seqs < 0 || heads <= 0 || D <= 0)
+    return SI_ERR_ARG;
+  if (heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_seqs == 0) return SI_OK;
   const int r = (D + si::DELTA_KS - 1) / si::DELTA_KS;
-#define SI_DELTA_CASE(R)                                                                        \
-  if (r <= R)                                                                                   \
-    return launch_delta_recurrence<T, R>(proj, proj_stride, prep, cu_q, seq_slots, state, o_out, \
-                                         n_seqs, heads, D, stream);
+#define SI_DELTA_CASE(R)                                                                          \
+  if (r <= R)                                                                                     \
+    return D % 4 == 0 ? launch_delta_recurrence<R, true>(prep, cu_q, seq_slots, state, o_out,     \
+                                                         n_seqs, heads, D, stream)                \
+                      : launch_delta_recurrence<R, false>(prep, cu_q, seq_slots, state, o_out,    \
+                                                          n_seqs, heads, D, stream);
   SI_DELTA_CASE(4)
   SI_DELTA_CASE(8)
   SI_DELTA_CASE(16)
@@ -221,24 +282,6 @@ static int delta_recurrence_by_size(const void* proj, int proj_stride, const flo
   SI_DELTA_CASE(64)
 #undef SI_DELTA_CASE
   return SI_ERR_UNSUPPORTED;  // heads of more than 256 channels
-}
-
-// state: [slots, heads, D, D] float32 (key channel, value channel); sequence s of the step owns
-// the tokens cu_q[s]..cu_q[s+1]-1 and the slot seq_slots[s].  o_out: [n_tokens, heads*D] float32.
-SI_API int si_delta_recurrence(const void* proj, int proj_stride, const float* prep, const int* cu_q,
-                               const int* seq_slots, float* state, float* o_out, int n_seqs,
-                               int heads, int D, int dtype, cudaStream_t stream) {
-  if (!proj || !prep || !cu_q || !seq_slots || !state || !o_out || n_seqs < 0 || heads <= 0 || D <= 0)
-    return SI_ERR_ARG;
-  if (heads > 65535) return SI_ERR_TOO_LARGE;
-  if (n_seqs == 0) return SI_OK;
-  if (dtype == SI_BF16)
-    return delta_recurrence_by_size<__nv_bfloat16>(proj, proj_stride, prep, cu_q, seq_slots, state,
-                                                   o_out, n_seqs, heads, D, stream);
-  if (dtype == SI_F32)
-    return delta_recurrence_by_size<float>(proj, proj_stride, prep, cu_q, seq_slots, state, o_out,
-                                           n_seqs, heads, D, stream);
-  return SI_ERR_DTYPE;
 }
 
 SI_API int si_delta_output(const float* o, const void* proj, int proj_stride, const void* gain,

@@ -19,22 +19,9 @@
 // row per token; the block cache a row per P tokens, row b of a request on page
 // table[b / rows] at offset b % rows.
 #include "common.cuh"
+#include "planes.cuh"
 
 namespace si {
-
-struct PlanesLayout {
-  int kv_heads, rows, kd, vd;
-  __device__ __forceinline__ long long page_elems() const {
-    return (long long)kv_heads * rows * (kd + vd);
-  }
-  __device__ __forceinline__ long long key_at(int page, int g, int row) const {
-    return (long long)page * page_elems() + ((long long)g * rows + row) * kd;
-  }
-  __device__ __forceinline__ long long value_at(int page, int g, int row) const {
-    return (long long)page * page_elems() + (long long)kv_heads * rows * kd +
-           ((long long)g * rows + row) * vd;
-  }
-};
 
 // ---------------------------------------------------------------- prepare
 // One block per token.  qkv row: [H*kd queries | G*kd keys | G*vd values].  Queries are

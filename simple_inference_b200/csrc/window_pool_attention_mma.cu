@@ -1,0 +1,339 @@
+// Window attention with pooled blocks on the tensor cores (bfloat16 storage, mma.sync
+// m16n8k16 with float32 accumulation; scores, softmax and the output sums are float32).
+//
+// A block works one tile of 16 consecutive tokens of one sequence for one key/value head; each
+// of its warps is one query head of that group, so the group's heads share every key and value
+// the block fetches.  The keys a tile can see are numbered x = 0 .. nb-1 (pooled blocks, nb
+// those seen by the tile's last token) and then the tokens from the first one that the tile's
+// first token sees to the tile's last token; they stream through two shared-memory stages of 64
+// keys (cp.async through the page tables of both caches), and each row masks what it does not
+// see: blocks not yet wholly before ITS window, tokens before its window or after itself.
+// A sequence that brings one token (decoding) is a tile with one row in use.
+// The same formulas as the generic kernel (window_pool_attention.cu), which stays the kernel of
+// float32 models and of head sizes that are no multiple of 16 or above 128.
+#include "common.cuh"
+#include "planes.cuh"
+
+namespace si {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int WPM_QT = 16;      // query rows of a tile
+constexpr int WPM_KT = 64;      // keys per stage
+constexpr int WPM_PAD = 8;      // elements added to a shared-memory row: no bank conflicts
+constexpr int WPM_MAX_WARPS = 4;
+
+__device__ __forceinline__ void wpm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void wpm_ldmatrix_x4_trans(uint32_t (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void wpm_cp16(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t wpm_pack(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// KD16: 16-wide steps of a key head the kernel has registers for; VD8: 8-wide tiles of a value
+// head.  The real sizes (multiples of 16, no larger) come in the layouts.
+template <int KD16, int VD8>
+__global__ void __launch_bounds__(32 * WPM_MAX_WARPS)
+wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __restrict__ positions,
+                        const int* __restrict__ cu_q, int n_seqs, const bf16* __restrict__ tok_pool,
+                        const int* __restrict__ tok_table, int tok_table_stride, PlanesLayout tl,
+                        const bf16* __restrict__ blk_pool, const int* __restrict__ blk_table,
+                        int blk_table_stride, PlanesLayout bl, bf16* __restrict__ out, int out_stride,
+                        int H, float scale, int W, int P, const float* __restrict__ freq_v) {
+  extern __shared__ __align__(16) unsigned char wpm_smem[];
+  const int kd = tl.kd, vd = tl.vd, G = tl.kv_heads;
+  const int kstride = kd + WPM_PAD, vstride = vd + WPM_PAD;
+  bf16* k_s = reinterpret_cast<bf16*>(wpm_smem);          // [2][KT][kstride]
+  bf16* v_s = k_s + 2 * WPM_KT * kstride;                 // [2][KT][vstride]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;                // row and column pair within a fragment
+
+  // which tile: sequences in order, ceil(tokens / 16) tiles each (the step's description was
+  // on the device before the step's first kernel)
+  int seq = -1, t0 = 0, nq = 0;
+  {
+    int b = blockIdx.x;
+    for (int s = 0; s < n_seqs; ++s) {
+      const int a = cu_q[s], e = cu_q[s + 1];
+      const int nt = (e - a + WPM_QT - 1) / WPM_QT;
+      if (b < nt) {
+        seq = s;
+        t0 = a + b * WPM_QT;
+        nq = min(WPM_QT, e - t0);
+        break;
+      }
+      b -= nt;
+    }
+  }
+  if (seq < 0) return;
+  const int g = blockIdx.y, Hg = H / G;
+  const int head_in_group = blockIdx.z * (int)(blockDim.x >> 5) + warp;
+  const bool active = head_in_group < Hg;
+  const int h = g * Hg + head_in_group;
+  const int p0 = positions[t0], p_last = p0 + nq - 1;
+  const int lo_min = (W > 0 && p0 - W + 1 > 0) ? p0 - W + 1 : 0;
+  const int nb_max = (W > 0 && P > 0 && p_last - W + 1 > 0) ? (p_last - W + 1) / P : 0;
+  const int n_slots = nb_max + (p_last - lo_min + 1);
+  const int n_tiles = (n_slots + WPM_KT - 1) / WPM_KT;
+  const int* ttab = tok_table + (size_t)seq * tok_table_stride;
+  const int* btab = blk_table ? blk_table + (size_t)seq * blk_table_stride : nullptr;
+  pdl_wait();
+
+  auto load_tile = [&](int i) {
+    const int st = i & 1;
+    const int kchunks = kd >> 3, per_row = (kd + vd) >> 3;
+    for (int idx = tid; idx < WPM_KT * per_row; idx += blockDim.x) {
+      const int row = idx / per_row, c = idx - row * per_row;
+      const int x = i * WPM_KT + row;
+      bf16* dst = c < kchunks ? k_s + (st * WPM_KT + row) * kstride + c * 8
+                              : v_s + (st * WPM_KT + row) * vstride + (c - kchunks) * 8;
+      if (x < n_slots) {
+        const bf16* src;
+        if (x < nb_max) {
+          const int page = btab[x / bl.rows], r = x % bl.rows;
+          src = c < kchunks ? blk_pool + bl.key_at(page, g, r) + c * 8
+                            : blk_pool + bl.value_at(page, g, r) + (c - kchunks) * 8;
+        } else {
+          const int j = lo_min + (x - nb_max);
+          const int page = ttab[j / tl.rows], r = j % tl.rows;
+          src = c < kchunks ? tok_pool + tl.key_at(page, g, r) + c * 8
+                            : tok_pool + tl.value_at(page, g, r) + (c - kchunks) * 8;
+        }
+        wpm_cp16(dst, src);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // a value row must not be garbage
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  load_tile(0);
+
+  // this warp's queries as A fragments: rows gq and gq+8 of the tile, all of the head's columns
+  uint32_t qf[KD16][4];
+#pragma unroll
+  for (int kk = 0; kk < KD16; ++kk) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = gq + (e & 1) * 8, col = kk * 16 + tq * 2 + (e >> 1) * 8;
+      uint32_t v = 0;
+      if (active && row < nq && col < kd)
+        v = *reinterpret_cast<const uint32_t*>(q + (size_t)(t0 + row) * q_stride + (size_t)h * kd + col);
+      qf[kk][e] = v;
+    }
+  }
+  // what each of this thread's two rows sees
+  int p_row[2], nb_row[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    p_row[r] = p0 + gq + r * 8;
+    nb_row[r] = (W > 0 && P > 0 && p_row[r] - W + 1 > 0) ? (p_row[r] - W + 1) / P : 0;
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  float o[VD8][4];
+#pragma unroll
+  for (int n = 0; n < VD8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.0f;
+
+  for (int i = 0; i < n_tiles; ++i) {
+    if (i + 1 < n_tiles) load_tile(i + 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    if (active) {
+      const bf16* ks = k_s + (i & 1) * WPM_KT * kstride;
+      const bf16* vs = v_s + (i & 1) * WPM_KT * vstride;
+      float s[WPM_KT / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < WPM_KT / 8; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < KD16; ++kk) {
+          if (kk * 16 < kd) {
+            const bf16* kp = ks + (nt * 8 + gq) * kstride + kk * 16 + tq * 2;
+            wpm_mma(s[nt], qf[kk], *reinterpret_cast<const uint32_t*>(kp),
+                    *reinterpret_cast<const uint32_t*>(kp + 8));
+          }
+        }
+      }
+      // scale and mask; row maxima
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < WPM_KT / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int x = i * WPM_KT + nt * 8 + tq * 2 + (e & 1);
+          bool vis;
+          if (x < nb_max) {
+            vis = x < nb_row[r];
+          } else {
+            const int j = lo_min + (x - nb_max);
+            vis = j <= p_row[r] && (W <= 0 || j > p_row[r] - W);
+          }
+          vis = vis && x < n_slots && gq + r * 8 < nq;
+          const float v = vis ? s[nt][e] * scale : -INFINITY;
+          s[nt][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = m_new == -INFINITY ? 0.0f : m_new;     // a row that has seen nothing yet
+        alpha[r] = __expf(m_run[r] - m_use[r]);            // exp(-inf) = 0 on the first tile
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int n = 0; n < VD8; ++n) {
+        o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int nt = 0; nt < WPM_KT / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = __expf(s[nt][e] - m_use[e >> 1]);
+          s[nt][e] = pv;
+          l_run[e >> 1] += pv;
+        }
+      }
+      // O += P V, 16 keys at a time; V fragments come transposed out of shared memory
+#pragma unroll
+      for (int kk = 0; kk < WPM_KT / 16; ++kk) {
+        uint32_t pa[4];
+        pa[0] = wpm_pack(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = wpm_pack(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = wpm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = wpm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int n2 = 0; n2 < VD8 / 2; ++n2) {
+          if (n2 * 16 < vd) {
+            const bf16* vp = vs + key * vstride + n2 * 16 + (lane >> 4) * 8;
+            uint32_t b[4];
+            wpm_ldmatrix_x4_trans(b, (unsigned)__cvta_generic_to_shared(vp));
+            wpm_mma(o[2 * n2], pa, b[0], b[1]);
+            wpm_mma(o[2 * n2 + 1], pa, b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the stage may be refilled
+  }
+  pdl_trigger();
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // normalise, hand the tile to shared memory, turn every head's rows back by their
+  // positions and store
+  float* o_s = reinterpret_cast<float*>(wpm_smem) + warp * WPM_QT * vd;   // [16][vd] of this warp
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+#pragma unroll
+    for (int n = 0; n < VD8; ++n) {
+      if (n * 8 < vd) {
+        const int col = n * 8 + tq * 2;
+        o_s[gq * vd + col] = o[n][0] * inv0;
+        o_s[gq * vd + col + 1] = o[n][1] * inv0;
+        o_s[(gq + 8) * vd + col] = o[n][2] * inv1;
+        o_s[(gq + 8) * vd + col + 1] = o[n][3] * inv1;
+      }
+    }
+    __syncwarp();
+    const int vhalf = vd >> 1;
+    for (int idx = lane; idx < nq * vd; idx += 32) {
+      const int row = idx / vd, d = idx - row * vd;
+      float x = o_s[idx];
+      if (freq_v) {
+        const int fi = d < vhalf ? d : d - vhalf;
+        float sn, cs;
+        sincosf((float)(p0 + row) * freq_v[fi], &sn, &cs);
+        const float y = o_s[row * vd + (d < vhalf ? d + vhalf : d - vhalf)];
+        x = d < vhalf ? x * cs + y * sn : x * cs - y * sn;
+      }
+      out[(size_t)(t0 + row) * out_stride + (size_t)h * vd + d] = __float2bfloat16_rn(x);
+    }
+  }
+}
+
+}  // namespace si
+
+template <int KD16, int VD8>
+static int launch_wp_attention_mma(const void* q, int q_stride, const int* positions, const int* cu_q,
+                                   int n_seqs, const void* tok_pool, const int* tok_table,
+                                   int tok_table_stride, si::PlanesLayout tl, const void* blk_pool,
+                                   const int* blk_table, int blk_table_stride, si::PlanesLayout bl,
+                                   void* out, int out_stride, int n_tokens, int H, float scale, int W,
+                                   int P, const float* freq_v, cudaStream_t stream) {
+  const int Hg = H / tl.kv_heads;
+  const int warps = Hg < si::WPM_MAX_WARPS ? Hg : si::WPM_MAX_WARPS;
+  const size_t smem = (size_t)2 * si::WPM_KT * (tl.kd + tl.vd + 2 * si::WPM_PAD) * sizeof(si::bf16);
+  auto kern = si::wp_attention_mma_kernel<KD16, VD8>;
+  if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
+  // an upper bound of the tiles: every sequence's last tile may be short
+  dim3 grid((n_tokens + si::WPM_QT - 1) / si::WPM_QT + n_seqs, tl.kv_heads, (Hg + warps - 1) / warps);
+  SI_LAUNCH(kern, grid, 32 * warps, smem, stream, (const si::bf16*)q, q_stride, positions, cu_q, n_seqs,
+            (const si::bf16*)tok_pool, tok_table, tok_table_stride, tl, (const si::bf16*)blk_pool,
+            blk_table, blk_table_stride, bl, (si::bf16*)out, out_stride, H, scale, W, P, freq_v);
+  return SI_OK;
+}
+
+// Whether the tensor-core kernel takes these head sizes (bfloat16 only).
+SI_API int si_wp_attention_mma_fits(int kd, int vd) {
+  return kd > 0 && vd > 0 && kd % 16 == 0 && vd % 16 == 0 && kd <= 128 && vd <= 128;
+}
+
+// Arguments as si_wp_attention, plus the sequences' token ranges cu_q[0..n_seqs]; bfloat16.
+SI_API int si_wp_attention_mma(const void* q, int q_stride, const int* positions, const int* cu_q,
+                               int n_seqs, const void* tok_pool, const int* tok_table,
+                               int tok_table_stride, int tok_rows, const void* blk_pool,
+                               const int* blk_table, int blk_table_stride, int blk_rows, void* out,
+                               int out_stride, int n_tokens, int H, int G, int kd, int vd, float scale,
+                               int W, int P, const float* freq_v, cudaStream_t stream) {
+  if (!q || !positions || !cu_q || !tok_pool || !tok_table || !out || n_tokens < 0 || n_seqs < 0 ||
+      H <= 0 || G <= 0 || H % G != 0 || tok_rows <= 0)
+    return SI_ERR_ARG;
+  if (!si_wp_attention_mma_fits(kd, vd)) return SI_ERR_UNSUPPORTED;
+  if (P > 0 && W > 0 && (!blk_pool || !blk_table || blk_rows <= 0)) return SI_ERR_ARG;
+  if (q_stride % 2 != 0 || ((uintptr_t)q & 3) || ((uintptr_t)tok_pool & 15) || ((uintptr_t)blk_pool & 15))
+    return SI_ERR_ARG;
+  if (G > 65535) return SI_ERR_TOO_LARGE;
+  if (n_tokens == 0 || n_seqs == 0) return SI_OK;
+  if (!blk_pool) P = 0;
+  si::PlanesLayout tl{G, tok_rows, kd, vd}, bl{G, blk_rows > 0 ? blk_rows : 1, kd, vd};
+#define SI_WPM_CASE(KD16, VD8)                                                                      \
+  if (kd <= 16 * KD16 && vd <= 8 * VD8)                                                             \
+    return launch_wp_attention_mma<KD16, VD8>(q, q_stride, positions, cu_q, n_seqs, tok_pool,       \
+                                              tok_table, tok_table_stride, tl, blk_pool, blk_table, \
+                                              blk_table_stride, bl, out, out_stride, n_tokens, H,   \
+                                              scale, W, P, freq_v, stream);
+  SI_WPM_CASE(4, 8)
+  SI_WPM_CASE(4, 16)
+  SI_WPM_CASE(8, 16)
+#undef SI_WPM_CASE
+  return SI_ERR_UNSUPPORTED;
+}

@@ -24,7 +24,8 @@ import torch
 from .build import KernelBuildError, load_library
 
 _CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tc.cu", "gemm_tc2.cu",
-                 "attention_generic.cu", "window_pool_attention.cu", "delta_rule.cu", "sampling.cu"]
+                 "attention_generic.cu", "window_pool_attention.cu", "window_pool_attention_mma.cu",
+                 "delta_rule.cu", "sampling.cu"]
 
 _ERRORS = {
     -1: "bad argument (null pointer, negative size or misaligned pointer)",
@@ -674,12 +675,31 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
                           blk_pool: torch.Tensor | None, blk_table: torch.Tensor | None,
                           blk_rows: int, out: torch.Tensor, num_q_heads: int, num_kv_heads: int,
                           key_dim: int, value_dim: int, scale: float, window: int | None,
-                          pool_size: int | None, freq_v: torch.Tensor | None) -> torch.Tensor:
+                          pool_size: int | None, freq_v: torch.Tensor | None,
+                          cu_q: torch.Tensor | None = None, n_seqs: int = 0) -> torch.Tensor:
     """Attention of every token over the last ``window`` tokens of its request and the pooled
-    blocks wholly before them, one softmax over both, float32 arithmetic; each head's output is
-    turned back by the query's position (``freq_v``; None leaves it).  ``q`` may be the fused
-    projection buffer: its first ``num_q_heads * key_dim`` columns are read."""
-    _dev(positions, tok_seq, tok_pool, tok_table, blk_pool, blk_table, out, freq_v)
+    blocks wholly before them, one softmax over both; each head's output is turned back by the
+    query's position (``freq_v``; None leaves it).  ``q`` may be the fused projection buffer:
+    its first ``num_q_heads * key_dim`` columns are read.
+
+    bfloat16 with head sizes that are multiples of 16 up to 128, and the sequences' token
+    ranges given (``cu_q``, ``n_seqs``): the tensor-core kernel, tiles of 16 tokens of a
+    sequence, float32 scores and sums.  Otherwise (float32 models, other sizes): the generic
+    kernel, float32 arithmetic throughout."""
+    _dev(positions, tok_seq, tok_pool, tok_table, blk_pool, blk_table, out, freq_v, cu_q)
+    if q.dtype == torch.bfloat16 and cu_q is not None and n_seqs > 0 and q.is_cuda and \
+            q.stride(1) == 1 and tok_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and \
+            out.shape[1] == num_q_heads * value_dim and q.stride(0) % 2 == 0 and \
+            core().si_wp_attention_mma_fits(key_dim, value_dim):
+        _i32(positions, "positions"); _i32(cu_q, "cu_q")
+        _i32(tok_table, "tok_table"); _i32(blk_table, "blk_table")
+        _check(core().si_wp_attention_mma(
+            _p(q), q.stride(0), _p(positions), _p(cu_q), n_seqs, _p(tok_pool), _p(tok_table),
+            tok_table.stride(0), tok_rows, _p(blk_pool), _p(blk_table),
+            0 if blk_table is None else blk_table.stride(0), blk_rows, _p(out), out.stride(0),
+            out.shape[0], num_q_heads, num_kv_heads, key_dim, value_dim, _c_float(scale),
+            int(window or 0), int(pool_size or 0), _p(freq_v), _stream()), "window_pool_attention_mma")
+        return out
     if not q.is_cuda or q.stride(1) != 1 or q.dtype != tok_pool.dtype or out.dtype != q.dtype:
         raise KernelError("window_pool_attention: q, the cache and out must share a dtype; q rows contiguous")
     _i32(positions, "positions"); _i32(tok_seq, "tok_seq")
@@ -698,34 +718,37 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
 
 # ------------------------------------------------------ generalised delta rule
 
-def delta_prepare(proj: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+def delta_prepare(proj: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
                   prep: torch.Tensor, num_heads: int, head_dim: int, rank: int) -> None:
-    """Per token, in float32: decay, unit key and rate times unit key of every head, from the
-    fused projection ``[r | k | v | g | a | low]`` (csrc/delta_rule.cu)."""
-    _dev(proj, w2, w0, a_bias, prep)
+    """Per token, in float32, six planes of the heads' width: decay, unit key, rate times unit
+    key, and k, r, v widened, from the fused projection ``[r | k | v | g | a | low]``;
+    ``w2t`` is the decay's second matrix transposed, ``[rank, heads*D]`` (csrc/delta_rule.cu)."""
+    _dev(proj, w2t, w0, a_bias, prep)
     n, hd = proj.shape[0], num_heads * head_dim
-    if proj.shape[1] != 5 * hd + rank or tuple(w2.shape) != (hd, rank) or w2.dtype != proj.dtype:
+    if proj.shape[1] != 5 * hd + rank or tuple(w2t.shape) != (rank, hd) or w2t.dtype != proj.dtype:
         raise KernelError("delta_prepare: projection or decay matrix does not fit")
     if w0.dtype != torch.float32 or a_bias.dtype != torch.float32 or w0.numel() != hd or \
-            a_bias.numel() != hd or prep.dtype != torch.float32 or tuple(prep.shape) != (n, 3 * hd):
+            a_bias.numel() != hd or prep.dtype != torch.float32 or tuple(prep.shape) != (n, 6 * hd):
         raise KernelError("delta_prepare: biases and output are float32 of the heads' width")
-    _check(core().si_delta_prepare(_p(proj), proj.stride(0), _p(w2), _p(w0), _p(a_bias), _p(prep), n,
+    _check(core().si_delta_prepare(_p(proj), proj.stride(0), _p(w2t), _p(w0), _p(a_bias), _p(prep), n,
                                    num_heads, head_dim, rank, _dt(proj), _stream()), "delta_prepare")
 
 
-def delta_recurrence(proj: torch.Tensor, prep: torch.Tensor, cu_q: torch.Tensor,
-                     seq_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, n_seqs: int,
-                     num_heads: int, head_dim: int) -> None:
-    """The scan over each sequence's tokens of the step; ``state`` ``[slots, heads, D, D]``
-    float32 is read at the sequence's slot and written back; ``out`` ``[tokens, heads*D]`` float32."""
-    _dev(proj, prep, cu_q, seq_slots, state, out)
+def delta_recurrence(prep: torch.Tensor, cu_q: torch.Tensor, seq_slots: torch.Tensor,
+                     state: torch.Tensor, out: torch.Tensor, n_seqs: int, num_heads: int,
+                     head_dim: int) -> None:
+    """The scan over each sequence's tokens of the step, from what ``delta_prepare`` wrote;
+    ``state`` ``[slots, heads, D, D]`` float32 is read at the sequence's slot and written back;
+    ``out`` ``[tokens, heads*D]`` float32."""
+    _dev(prep, cu_q, seq_slots, state, out)
     _i32(cu_q, "cu_q"); _i32(seq_slots, "seq_slots")
+    hd = num_heads * head_dim
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (num_heads, head_dim, head_dim) \
-            or out.dtype != torch.float32 or out.shape[1] != num_heads * head_dim:
-        raise KernelError("delta_recurrence: state or output does not fit")
-    _check(core().si_delta_recurrence(_p(proj), proj.stride(0), _p(prep), _p(cu_q), _p(seq_slots),
-                                      _p(state), _p(out), n_seqs, num_heads, head_dim, _dt(proj),
-                                      _stream()), "delta_recurrence")
+            or out.dtype != torch.float32 or out.shape[1] != hd or prep.dtype != torch.float32 \
+            or tuple(prep.shape) != (out.shape[0], 6 * hd):
+        raise KernelError("delta_recurrence: state, inputs or output do not fit")
+    _check(core().si_delta_recurrence(_p(prep), _p(cu_q), _p(seq_slots), _p(state), _p(out), n_seqs,
+                                      num_heads, head_dim, _stream()), "delta_recurrence")
 
 
 def delta_output(o: torch.Tensor, proj: torch.Tensor, gain: torch.Tensor, out: torch.Tensor,

@@ -60,7 +60,7 @@ class GeneralDelta(Mixer):
         super().bind(tensors, rt)
         self.w_proj = torch.cat([tensors[n] for n in ("r", "k", "v", "g", "a", "w1")],
                                 dim=0).contiguous()
-        self.w2 = tensors["w2"].contiguous()
+        self.w2t = tensors["w2"].t().contiguous()   # [rank, width]: channels side by side
         self.w0 = tensors["w0"].float().contiguous()
         self.a_bias = tensors["a_bias"].float().contiguous()
         self.gain = tensors["norm"].contiguous()
@@ -70,11 +70,11 @@ class GeneralDelta(Mixer):
         n = x.shape[0]
         proj = ctx.ws.get("delta.proj", (n, 5 * self.width + self.rank), x.dtype)
         ops.linear(x, self.w_proj, proj)
-        prep = ctx.ws.get("delta.prep", (n, 3 * self.width), torch.float32)
-        ops.delta_prepare(proj, self.w2, self.w0, self.a_bias, prep, self.num_heads, self.head_dim,
+        prep = ctx.ws.get("delta.prep", (n, 6 * self.width), torch.float32)
+        ops.delta_prepare(proj, self.w2t, self.w0, self.a_bias, prep, self.num_heads, self.head_dim,
                           self.rank)
         o = ctx.ws.get("delta.o", (n, self.width), torch.float32)
-        ops.delta_recurrence(proj, prep, ctx.cu_q, ctx.seq_slots, cache.state, o, ctx.n_seqs,
+        ops.delta_recurrence(prep, ctx.cu_q, ctx.seq_slots, cache.state, o, ctx.n_seqs,
                              self.num_heads, self.head_dim)
         mixed = ctx.ws.get("delta.mixed", (n, self.width), x.dtype)
         ops.delta_output(o, proj, self.gain, mixed, self.num_heads, self.head_dim, self.eps)

@@ -122,6 +122,6 @@ class PooledWindowAttention(Mixer):
         ops.window_pool_attention(qkv, ctx.positions, ctx.tok_seq, tok.pool, tok_table, tok_rows,
                                   blk_pool, blk_table, blk_rows, mixed, self.num_heads,
                                   self.num_kv_heads, self.key_dim, self.value_dim, self.scale,
-                                  self.window, self.pool, self.freq_v)
+                                  self.window, self.pool, self.freq_v, ctx.cu_q, ctx.n_seqs)
         return ops.linear_for_residual(mixed, self.w_o, ctx.ws, "wpattn.proj",
                                        getattr(ctx, "partial_sums_ok", False))

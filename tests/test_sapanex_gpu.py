@@ -213,3 +213,66 @@ def test_pages_and_slots_that_are_used_again(models, dtype):
             grp.allocator.check()
     assert max(len(v) for v in seen_pages.values()) >= 4
     assert all(len(v) >= 3 for v in seen_slots.values()) and len(seen_slots) == 2
+
+
+# ------------------------------------------- the tensor-core attention kernel by itself
+
+def _paged_case(G, kd, vd, W, P, seqs, seed, rows=16, blk_rows=4):
+    """Random queries and caches for sequences given as (context length, tokens in the step).
+    Pages are handed out in random order; table entries before what a step may read point at
+    a page of huge values, so that a read outside the window shows."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum((c + rows - 1) // rows for c, _ in seqs) + 1
+    n_bpages = sum((c // P + blk_rows - 1) // blk_rows + 1 for c, _ in seqs) + 1
+    tok_pool = torch.randn(n_pages, G * rows * (kd + vd), generator=g)
+    blk_pool = torch.randn(n_bpages, G * blk_rows * (kd + vd), generator=g)
+    tok_pool[0] = 3e4; blk_pool[0] = 3e4                    # the poisoned pages
+    free = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+    bfree = (torch.randperm(n_bpages - 1, generator=g) + 1).tolist()
+    max_pages = max((c + rows - 1) // rows for c, _ in seqs)
+    max_bpages = max((c // P + blk_rows - 1) // blk_rows + 1 for c, _ in seqs)
+    tok_table = torch.zeros(len(seqs), max_pages, dtype=torch.int32)
+    blk_table = torch.zeros(len(seqs), max_bpages, dtype=torch.int32)
+    positions, tok_seq, cu_q = [], [], [0]
+    for s, (ctx, nq) in enumerate(seqs):
+        first = max(0, ctx - nq - W + 1)                    # first token any query of the step sees
+        for lp in range(first // rows, (ctx + rows - 1) // rows):
+            tok_table[s, lp] = free.pop()
+        n_blocks = max(0, (ctx - 1 - W + 1)) // P           # blocks the last query sees
+        for lp in range((n_blocks + blk_rows - 1) // blk_rows):
+            blk_table[s, lp] = bfree.pop()
+        positions += list(range(ctx - nq, ctx))
+        tok_seq += [s] * nq
+        cu_q.append(cu_q[-1] + nq)
+    return dict(tok_pool=tok_pool, blk_pool=blk_pool, tok_table=tok_table, blk_table=blk_table,
+                positions=torch.tensor(positions, dtype=torch.int32),
+                tok_seq=torch.tensor(tok_seq, dtype=torch.int32),
+                cu_q=torch.tensor(cu_q, dtype=torch.int32), rows=rows, blk_rows=blk_rows)
+
+
+@pytest.mark.parametrize("H,G,kd,vd,W,P", [(8, 2, 64, 80, 40, 8), (3, 1, 128, 128, 24, 5),
+                                             (10, 2, 16, 32, 7, 16), (4, 4, 32, 16, 100, 3)])
+def test_tensor_core_attention_equals_the_generic_kernel(H, G, kd, vd, W, P):
+    """Portions of prompts (from position 0, in mid-sequence, over page borders), single decoded
+    tokens and a first token in one batch; bfloat16 caches; the generic kernel, which the other
+    tests hold against the plain implementation, is the yardstick."""
+    from simple_inference_b200 import ops
+    seqs = [(300, 37), (1, 1), (150, 1), (64, 64), (500, 16), (W + P, 1), (W + P - 1, 1), (33, 17)]
+    case = _paged_case(G, kd, vd, W, P, seqs, seed=kd + W)
+    n = int(case["cu_q"][-1])
+    g = torch.Generator().manual_seed(1)
+    q = (torch.randn(n, H * kd + 24, generator=g) * 1.5).to(torch.bfloat16).cuda()
+    freq_v = (10000.0 ** (-torch.arange(vd // 2, dtype=torch.float64) * 2 / vd)).float().cuda()
+    dev = {k: (v.to(torch.bfloat16).cuda() if v.dtype == torch.float32 else v.cuda())
+           for k, v in case.items() if isinstance(v, torch.Tensor)}
+    outs = []
+    for cu_q in (None, dev["cu_q"]):
+        out = torch.zeros(n, H * vd, dtype=torch.bfloat16, device="cuda")
+        ops.window_pool_attention(q, dev["positions"], dev["tok_seq"], dev["tok_pool"], dev["tok_table"],
+                                  case["rows"], dev["blk_pool"], dev["blk_table"], case["blk_rows"], out,
+                                  H, G, kd, vd, 0.6 / kd ** 0.5 * 4, W, P, freq_v, cu_q, len(seqs))
+        outs.append(out.float().cpu())
+    generic, fast = outs
+    assert torch.isfinite(fast).all() and generic.abs().max() < 100   # nobody read a poisoned page
+    assert (fast - generic).abs().max() < 0.04 * generic.abs().max()
+    assert relative_error(fast, generic) < 0.03
