@@ -50,6 +50,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride
   const float ss = block_sum(k * k, red);  // also orders low_s
   if (!mine) return;
   float z = z0;
+#pragma unroll 8
   for (int l = 0; l < L; ++l) z = fmaf(to_f32<T>(w2t[(size_t)l * HD + col]), low_s[l], z);
   const float decay = expf(-0.60653065971263342f * sigmoidf_(z));
   const float u = k / sqrtf(ss + 1e-6f);
@@ -64,7 +65,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride
 }
 
 // Threads of a block: DC value channels x KS lanes; lane ks of channel d keeps S[c][d] for
-// c = ks + KS*i, i < R, in registers (c >= D padded with zeros).  Tokens are taken in groups
+// c = ks*R + i, i < R, in registers (c >= D padded with zeros).  Tokens are taken in groups
 // of TB; a group's inputs ([TB][5][Dp] key-side planes and [TB][DC] values) are one stage of a
 // ring of NS stages that cp.async fills NS-1 groups ahead of the arithmetic.
 constexpr int DELTA_KS = 4;    // lanes that share one value channel
@@ -109,10 +110,10 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
   pdl_wait();
   pdl_trigger();
   float* S_g = state + ((size_t)slot * heads + h) * D * D;
-  float S[R];
+  float S[R];   // lane ks owns the key channels ks*R .. ks*R + R - 1 of its column
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int c = ks + DELTA_KS * i;
+    const int c = ks * R + i;
     S[i] = (col_ok && c < D) ? S_g[(size_t)c * D + d] : 0.0f;
   }
   const int n_groups = (t_end - t_begin + DELTA_TB - 1) / DELTA_TB;
@@ -151,6 +152,48 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
     }
     cp_async_commit();   // an empty group keeps the count uniform
   };
+
+  // One token: in[p] holds this lane's R channels of plane p (decay, u, rate*u, k, r).  Four
+  // running sums keep the chains of dependent additions short; the order of the additions is
+  // fixed, so the result does not depend on where the token sits in a step.
+  constexpr int R4 = R / 4;
+  auto token = [&](const float4 (&in)[5][R4], float v, int t) {
+    float us[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < R4; ++j) {
+      us[0] = fmaf(in[1][j].x, S[4 * j], us[0]);
+      us[1] = fmaf(in[1][j].y, S[4 * j + 1], us[1]);
+      us[2] = fmaf(in[1][j].z, S[4 * j + 2], us[2]);
+      us[3] = fmaf(in[1][j].w, S[4 * j + 3], us[3]);
+    }
+    float ust = (us[0] + us[1]) + (us[2] + us[3]);
+#pragma unroll
+    for (int o = DELTA_KS / 2; o > 0; o >>= 1) ust += __shfl_xor_sync(0xffffffffu, ust, o);
+    float os[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < R4; ++j) {
+      S[4 * j] = fmaf(in[0][j].x, S[4 * j], fmaf(in[3][j].x, v, -in[2][j].x * ust));
+      S[4 * j + 1] = fmaf(in[0][j].y, S[4 * j + 1], fmaf(in[3][j].y, v, -in[2][j].y * ust));
+      S[4 * j + 2] = fmaf(in[0][j].z, S[4 * j + 2], fmaf(in[3][j].z, v, -in[2][j].z * ust));
+      S[4 * j + 3] = fmaf(in[0][j].w, S[4 * j + 3], fmaf(in[3][j].w, v, -in[2][j].w * ust));
+      os[0] = fmaf(S[4 * j], in[4][j].x, os[0]);
+      os[1] = fmaf(S[4 * j + 1], in[4][j].y, os[1]);
+      os[2] = fmaf(S[4 * j + 2], in[4][j].z, os[2]);
+      os[3] = fmaf(S[4 * j + 3], in[4][j].w, os[3]);
+    }
+    float ot = (os[0] + os[1]) + (os[2] + os[3]);
+#pragma unroll
+    for (int off = DELTA_KS / 2; off > 0; off >>= 1) ot += __shfl_xor_sync(0xffffffffu, ot, off);
+    if (ks == 0 && col_ok) o_out[(size_t)t * HD + h * D + d] = ot;
+  };
+  auto read = [&](float4 (&in)[5][R4], const float* st, int tt) {
+    const float4* base = reinterpret_cast<const float4*>(st + tt * 5 * Dp + ks * R);
+#pragma unroll
+    for (int pl = 0; pl < 5; ++pl)
+#pragma unroll
+      for (int j = 0; j < R4; ++j) in[pl][j] = base[pl * (Dp / 4) + j];
+  };
+
 #pragma unroll
   for (int g = 0; g < DELTA_NS - 1; ++g) fetch(g);
   for (int g = 0; g < n_groups; ++g) {
@@ -161,41 +204,32 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
     const float* v_s = st + DELTA_TB * 5 * Dp;
     const int tb = t_begin + g * DELTA_TB;
     const int nt = min(DELTA_TB, t_end - tb);
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* w_s = st + tt * 5 * Dp;
-      const float* u_s = w_s + Dp;
-      const float* au_s = w_s + 2 * Dp;
-      const float* k_s = w_s + 3 * Dp;
-      const float* r_s = w_s + 4 * Dp;
-      float us0 = 0.0f, us1 = 0.0f;
-#pragma unroll
-      for (int i = 0; i < R; i += 2) {
-        us0 = fmaf(u_s[ks + DELTA_KS * i], S[i], us0);
-        if (i + 1 < R) us1 = fmaf(u_s[ks + DELTA_KS * (i + 1)], S[i + 1], us1);
+    if (R <= 16) {
+      // two sets of registers: the next token's inputs leave shared memory while this
+      // token's sums run
+      float4 a[5][R4], b[5][R4];
+      read(a, st, 0);
+      for (int tt = 0; tt < nt; tt += 2) {
+        if (tt + 1 < nt) read(b, st, tt + 1);
+        token(a, v_s[tt * DELTA_DC + dl], tb + tt);
+        if (tt + 1 < nt) {
+          if (tt + 2 < nt) read(a, st, tt + 2);
+          token(b, v_s[(tt + 1) * DELTA_DC + dl], tb + tt + 1);
+        }
       }
-      float us = us0 + us1;
-#pragma unroll
-      for (int o = DELTA_KS / 2; o > 0; o >>= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
-      const float v = v_s[tt * DELTA_DC + dl];
-      float o0 = 0.0f, o1 = 0.0f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int c = ks + DELTA_KS * i;
-        S[i] = fmaf(w_s[c], S[i], fmaf(k_s[c], v, -au_s[c] * us));
-        if (i & 1) o1 = fmaf(S[i], r_s[c], o1);
-        else o0 = fmaf(S[i], r_s[c], o0);
+    } else {
+      float4 a[5][R4];
+      for (int tt = 0; tt < nt; ++tt) {
+        read(a, st, tt);
+        token(a, v_s[tt * DELTA_DC + dl], tb + tt);
       }
-      float o = o0 + o1;
-#pragma unroll
-      for (int off = DELTA_KS / 2; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (ks == 0 && col_ok) o_out[(size_t)(tb + tt) * HD + h * D + d] = o;
     }
     __syncthreads();   // the stage may be refilled
   }
   cp_async_wait<0>();
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int c = ks + DELTA_KS * i;
+    const int c = ks * R + i;
     if (col_ok && c < D) S_g[(size_t)c * D + d] = S[i];
   }
 }
