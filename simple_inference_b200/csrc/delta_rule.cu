@@ -66,9 +66,10 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride
 
 // Threads of a block: DC value channels x KS lanes; lane ks of channel d keeps S[c][d] for
 // c = ks*R + i, i < R, in registers (c >= D padded with zeros).  Tokens are taken in groups
-// of TB; a group's inputs ([TB][5][Dp] key-side planes and [TB][DC] values) are one stage of a
-// ring of NS stages that cp.async fills NS-1 groups ahead of the arithmetic.
-constexpr int DELTA_KS = 4;    // lanes that share one value channel
+// of TB; a group's inputs ([TB][5] key-side planes and [TB][DC] values) are one stage of a
+// ring of NS stages that cp.async fills NS-1 groups ahead of the arithmetic.  In a plane each
+// lane's R channels are followed by four unused words, so that the lanes' 16-byte reads fall
+// into different banks.
 constexpr int DELTA_DC = 32;   // value channels per block
 constexpr int DELTA_TB = 8;    // tokens per stage
 constexpr int DELTA_NS = 4;    // stages
@@ -86,18 +87,25 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int R, bool VEC>
-__global__ void __launch_bounds__(DELTA_KS * DELTA_DC)
+template <int R, int KS>
+struct DeltaShape {
+  static constexpr int PLANE = KS * (R + 4);                       // words of one plane of one token
+  static constexpr int STAGE = DELTA_TB * (5 * PLANE + DELTA_DC);  // words of a stage
+  __host__ __device__ static constexpr int at(int c) { return (c / R) * (R + 4) + (c % R); }
+};
+
+template <int R, int KS, bool VEC>
+__global__ void __launch_bounds__(KS * DELTA_DC)
 delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ cu_q,
                         const int* __restrict__ seq_slots, float* __restrict__ state,
                         float* __restrict__ o_out, int heads, int D) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int Dp = R * DELTA_KS;                      // padded number of key channels
-  constexpr int STAGE = DELTA_TB * (5 * Dp + DELTA_DC);  // floats per stage
+  using Sh = DeltaShape<R, KS>;
+  constexpr int PLANE = Sh::PLANE, STAGE = Sh::STAGE, V_AT = DELTA_TB * 5 * PLANE;
   const int s = blockIdx.x, h = blockIdx.y;
   const int d0 = blockIdx.z * DELTA_DC;
   const int tid = threadIdx.x;
-  const int ks = tid % DELTA_KS, dl = tid / DELTA_KS;
+  const int ks = tid % KS, dl = tid / KS;
   const int d = d0 + dl;
   const bool col_ok = d < D;
   const int HD = heads * D;
@@ -106,6 +114,28 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
   const int slot = seq_slots[s];                        // before the step's first kernel
   // channels past D (and value channels past the head's) stay zero in every stage
   for (int i = tid; i < DELTA_NS * STAGE; i += blockDim.x) sm[i] = 0.0f;
+  // what this thread copies for every token (16-byte runs): found once
+  constexpr int NF = 2;
+  int f_src[NF], f_dst[NF], f_step[NF];
+  if (VEC) {
+    const int per_plane = D / 4, per_tok = 5 * per_plane + (dc + 3) / 4;
+#pragma unroll
+    for (int n = 0; n < NF; ++n) {
+      const int e = tid + n * (int)blockDim.x;
+      f_src[n] = -1; f_dst[n] = 0; f_step[n] = 0;
+      if (e < 5 * per_plane) {
+        const int which = e / per_plane, c4 = (e - which * per_plane) * 4;
+        f_src[n] = which * HD + c4;
+        f_dst[n] = which * PLANE + Sh::at(c4);
+        f_step[n] = 5 * PLANE;
+      } else if (e < per_tok) {
+        const int c4 = (e - 5 * per_plane) * 4;
+        f_src[n] = 5 * HD + d0 + c4;
+        f_dst[n] = V_AT + c4;
+        f_step[n] = DELTA_DC;
+      }
+    }
+  }
   __syncthreads();
   pdl_wait();
   pdl_trigger();
@@ -122,19 +152,14 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
       float* st = sm + (g % DELTA_NS) * STAGE;
       const int tb = t_begin + g * DELTA_TB;
       const int nt = min(DELTA_TB, t_end - tb);
-      if (VEC) {   // D is a multiple of 4: every run below starts on a 16-byte boundary
-        const int per_plane = D / 4, per_tok = 5 * per_plane + (dc + 3) / 4;
-        for (int idx = tid; idx < nt * per_tok; idx += blockDim.x) {
-          const int tt = idx / per_tok, e = idx - tt * per_tok;
-          const float* src = prep + (size_t)(tb + tt) * DELTA_PLANES * HD + h * D;
-          if (e < 5 * per_plane) {
-            const int which = e / per_plane, c4 = (e - which * per_plane) * 4;
-            cp_async16(st + (tt * 5 + which) * Dp + c4, src + (size_t)which * HD + c4);
-          } else {
-            const int c4 = (e - 5 * per_plane) * 4;
-            cp_async16(st + DELTA_TB * 5 * Dp + tt * DELTA_DC + c4, src + (size_t)5 * HD + d0 + c4);
-          }
-        }
+      if (VEC) {   // D is a multiple of 4: every run starts on a 16-byte boundary
+        const float* src = prep + (size_t)tb * DELTA_PLANES * HD + h * D;
+#pragma unroll
+        for (int n = 0; n < NF; ++n)
+          if (f_src[n] >= 0)
+            for (int tt = 0; tt < nt; ++tt)
+              cp_async16(st + f_dst[n] + tt * f_step[n],
+                         src + (size_t)tt * DELTA_PLANES * HD + f_src[n]);
       } else {
         const int per_tok = 5 * D + dc;
         for (int idx = tid; idx < nt * per_tok; idx += blockDim.x) {
@@ -142,10 +167,10 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
           const float* src = prep + (size_t)(tb + tt) * DELTA_PLANES * HD + h * D;
           if (e < 5 * D) {
             const int which = e / D, c = e - which * D;
-            cp_async4(st + (tt * 5 + which) * Dp + c, src + (size_t)which * HD + c);
+            cp_async4(st + (tt * 5 + which) * PLANE + Sh::at(c), src + (size_t)which * HD + c);
           } else {
             const int c = e - 5 * D;
-            cp_async4(st + DELTA_TB * 5 * Dp + tt * DELTA_DC + c, src + (size_t)5 * HD + d0 + c);
+            cp_async4(st + V_AT + tt * DELTA_DC + c, src + (size_t)5 * HD + d0 + c);
           }
         }
       }
@@ -168,7 +193,7 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
     }
     float ust = (us[0] + us[1]) + (us[2] + us[3]);
 #pragma unroll
-    for (int o = DELTA_KS / 2; o > 0; o >>= 1) ust += __shfl_xor_sync(0xffffffffu, ust, o);
+    for (int o = KS / 2; o > 0; o >>= 1) ust += __shfl_xor_sync(0xffffffffu, ust, o);
     float os[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int j = 0; j < R4; ++j) {
@@ -183,15 +208,15 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
     }
     float ot = (os[0] + os[1]) + (os[2] + os[3]);
 #pragma unroll
-    for (int off = DELTA_KS / 2; off > 0; off >>= 1) ot += __shfl_xor_sync(0xffffffffu, ot, off);
+    for (int off = KS / 2; off > 0; off >>= 1) ot += __shfl_xor_sync(0xffffffffu, ot, off);
     if (ks == 0 && col_ok) o_out[(size_t)t * HD + h * D + d] = ot;
   };
   auto read = [&](float4 (&in)[5][R4], const float* st, int tt) {
-    const float4* base = reinterpret_cast<const float4*>(st + tt * 5 * Dp + ks * R);
+    const float4* base = reinterpret_cast<const float4*>(st + tt * 5 * PLANE + ks * (R + 4));
 #pragma unroll
     for (int pl = 0; pl < 5; ++pl)
 #pragma unroll
-      for (int j = 0; j < R4; ++j) in[pl][j] = base[pl * (Dp / 4) + j];
+      for (int j = 0; j < R4; ++j) in[pl][j] = base[pl * (PLANE / 4) + j];
   };
 
 #pragma unroll
@@ -201,7 +226,7 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
     cp_async_wait<DELTA_NS - 1>();    // this thread's copies of group g have landed
     __syncthreads();                  // and everyone else's
     const float* st = sm + (g % DELTA_NS) * STAGE;
-    const float* v_s = st + DELTA_TB * 5 * Dp;
+    const float* v_s = st + V_AT;
     const int tb = t_begin + g * DELTA_TB;
     const int nt = min(DELTA_TB, t_end - tb);
     if (R <= 16) {
@@ -278,23 +303,22 @@ SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2t, 
   return SI_OK;
 }
 
-template <int R, bool VEC>
+template <int R, int KS, bool VEC>
 static int launch_delta_recurrence(const float* prep, const int* cu_q, const int* seq_slots,
                                    float* state, float* o_out, int n_seqs, int heads, int D,
                                    cudaStream_t stream) {
-  const size_t smem = (size_t)si::DELTA_NS * si::DELTA_TB * (5 * R * si::DELTA_KS + si::DELTA_DC) *
-                      sizeof(float);
-  auto kern = si::delta_recurrence_kernel<R, VEC>;
+  const size_t smem = (size_t)si::DELTA_NS * si::DeltaShape<R, KS>::STAGE * sizeof(float);
+  auto kern = si::delta_recurrence_kernel<R, KS, VEC>;
   if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
   dim3 grid(n_seqs, heads, (D + si::DELTA_DC - 1) / si::DELTA_DC);
-  SI_LAUNCH(kern, grid, si::DELTA_KS * si::DELTA_DC, smem, stream, prep, cu_q, seq_slots, state,
-            o_out, heads, D);
+  SI_LAUNCH(kern, grid, KS * si::DELTA_DC, smem, stream, prep, cu_q, seq_slots, state, o_out, heads, D);
   return SI_OK;
 }
 
 // state: [slots, heads, D, D] float32 (key channel, value channel); sequence s of the step owns
 // the tokens cu_q[s]..cu_q[s+1]-1 and the slot seq_slots[s].  prep: what si_delta_prepare
-// wrote.  o_out: [n_tokens, heads*D] float32.
+// wrote.  o_out: [n_tokens, heads*D] float32.  Heads of 32 channels and more spread a column's
+// key channels over eight lanes, smaller ones over four.
 SI_API int si_delta_recurrence(const float* prep, const int* cu_q, const int* seq_slots,
                                float* state, float* o_out, int n_seqs, int heads, int D,
                                cudaStream_t stream) {
@@ -302,18 +326,17 @@ SI_API int si_delta_recurrence(const float* prep, const int* cu_q, const int* se
     return SI_ERR_ARG;
   if (heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_seqs == 0) return SI_OK;
-  const int r = (D + si::DELTA_KS - 1) / si::DELTA_KS;
-#define SI_DELTA_CASE(R)                                                                          \
-  if (r <= R)                                                                                     \
-    return D % 4 == 0 ? launch_delta_recurrence<R, true>(prep, cu_q, seq_slots, state, o_out,     \
-                                                         n_seqs, heads, D, stream)                \
-                      : launch_delta_recurrence<R, false>(prep, cu_q, seq_slots, state, o_out,    \
-                                                          n_seqs, heads, D, stream);
-  SI_DELTA_CASE(4)
-  SI_DELTA_CASE(8)
-  SI_DELTA_CASE(16)
-  SI_DELTA_CASE(32)
-  SI_DELTA_CASE(64)
+#define SI_DELTA_CASE(R, KS)                                                                       \
+  if (D <= R * KS)                                                                                 \
+    return D % 4 == 0 ? launch_delta_recurrence<R, KS, true>(prep, cu_q, seq_slots, state, o_out,  \
+                                                             n_seqs, heads, D, stream)             \
+                      : launch_delta_recurrence<R, KS, false>(prep, cu_q, seq_slots, state, o_out, \
+                                                              n_seqs, heads, D, stream);
+  SI_DELTA_CASE(4, 4)
+  SI_DELTA_CASE(4, 8)
+  SI_DELTA_CASE(8, 8)
+  SI_DELTA_CASE(16, 8)
+  SI_DELTA_CASE(32, 8)
 #undef SI_DELTA_CASE
   return SI_ERR_UNSUPPORTED;  // heads of more than 256 channels
 }
