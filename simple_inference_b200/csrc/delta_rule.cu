@@ -27,41 +27,73 @@ constexpr int DELTA_PLANES = 6;   // prep[t][plane][heads*D]: decay, u, rate*u, 
 
 // proj columns: [r | k | v | g | a | low], each of the first five HD = heads*D wide, low L wide.
 // w2t is the decay's second matrix transposed, [L, HD], so that neighbouring channels read
-// neighbouring words.
-template <typename T>
+// neighbouring words.  A block takes TG tokens of one head: with many tokens (prompts) a word of
+// w2t serves eight of them, with few (decoding) every token has blocks of its own.
+template <typename T, int TG>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride,
                                      const T* __restrict__ w2t, const float* __restrict__ w0,
                                      const float* __restrict__ a_bias, float* __restrict__ prep,
-                                     int heads, int D, int L) {
-  extern __shared__ float low_s[];  // [L] tanh of the inner projection
-  __shared__ float red[32];
-  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+                                     int n_tokens, int heads, int D, int L) {
+  extern __shared__ float low_s[];             // [TG][L] tanh of the inner projection
+  __shared__ float part[TG][32];               // per token: the warps' sums of k^2
+  const int t0 = blockIdx.x * TG, h = blockIdx.y, c = threadIdx.x;
+  const int nt = min(TG, n_tokens - t0);
   const int HD = heads * D;
   const bool mine = c < D;
   const int col = h * D + c;
+  const int lane = c & 31, warp = c >> 5, n_warps = (blockDim.x + 31) >> 5;
   // weights first: no kernel of the step writes them
   const float bias = mine ? a_bias[col] : 0.0f;
   const float z0 = mine ? w0[col] : 0.0f;
   pdl_wait();
   pdl_trigger();
-  const T* row = proj + (size_t)t * proj_stride;
-  for (int l = threadIdx.x; l < L; l += blockDim.x) low_s[l] = tanhf(to_f32<T>(row[5 * HD + l]));
-  const float k = mine ? to_f32<T>(row[HD + col]) : 0.0f;
-  const float ss = block_sum(k * k, red);  // also orders low_s
+  for (int idx = threadIdx.x; idx < TG * L; idx += blockDim.x) {
+    const int tt = idx / L, l = idx - tt * L;
+    low_s[idx] = tt < nt ? tanhf(to_f32<T>(proj[(size_t)(t0 + tt) * proj_stride + 5 * HD + l])) : 0.0f;
+  }
+  float k[TG], r_in[TG], v_in[TG], a_in[TG];
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt) {
+    const bool on = mine && tt < nt;
+    const T* row = proj + (size_t)(t0 + (tt < nt ? tt : 0)) * proj_stride;
+    k[tt] = on ? to_f32<T>(row[HD + col]) : 0.0f;
+    r_in[tt] = on ? to_f32<T>(row[col]) : 0.0f;
+    v_in[tt] = on ? to_f32<T>(row[2 * HD + col]) : 0.0f;
+    a_in[tt] = on ? to_f32<T>(row[4 * HD + col]) : 0.0f;
+  }
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt) {
+    const float sq = warp_sum(k[tt] * k[tt]);
+    if (lane == 0) part[tt][warp] = sq;
+  }
+  __syncthreads();   // low_s and part are complete
   if (!mine) return;
-  float z = z0;
+  float z[TG];
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt) z[tt] = z0;
 #pragma unroll 8
-  for (int l = 0; l < L; ++l) z = fmaf(to_f32<T>(w2t[(size_t)l * HD + col]), low_s[l], z);
-  const float decay = expf(-0.60653065971263342f * sigmoidf_(z));
-  const float u = k / sqrtf(ss + 1e-6f);
-  const float rate = sigmoidf_(to_f32<T>(row[4 * HD + col]) + bias);
-  float* dst = prep + (size_t)t * DELTA_PLANES * HD + col;
-  dst[0] = decay;
-  dst[HD] = u;
-  dst[2 * HD] = rate * u;
-  dst[3 * HD] = k;
-  dst[4 * HD] = to_f32<T>(row[col]);
-  dst[5 * HD] = to_f32<T>(row[2 * HD + col]);
+  for (int l = 0; l < L; ++l) {
+    const float w = to_f32<T>(w2t[(size_t)l * HD + col]);
+#pragma unroll
+    for (int tt = 0; tt < TG; ++tt) z[tt] = fmaf(w, low_s[tt * L + l], z[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt) {
+    if (tt < nt) {
+      float ss = 0.0f;
+      for (int w = 0; w < n_warps; ++w) ss += part[tt][w];   // fixed order
+      const float decay = expf(-0.60653065971263342f * sigmoidf_(z[tt]));
+      const float u = k[tt] / sqrtf(ss + 1e-6f);
+      const float rate = sigmoidf_(a_in[tt] + bias);
+      float* dst = prep + (size_t)(t0 + tt) * DELTA_PLANES * HD + col;
+      dst[0] = decay;
+      dst[HD] = u;
+      dst[2 * HD] = rate * u;
+      dst[3 * HD] = k[tt];
+      dst[4 * HD] = r_in[tt];
+      dst[5 * HD] = v_in[tt];
+    }
+  }
 }
 
 // Threads of a block: DC value channels x KS lanes; lane ks of channel d keeps S[c][d] for
@@ -280,6 +312,19 @@ __global__ void delta_output_kernel(const float* __restrict__ o, const T* __rest
 
 }  // namespace si
 
+template <typename T, int TG>
+static int launch_delta_prepare(const void* proj, int proj_stride, const void* w2t, const float* w0,
+                                const float* a_bias, float* prep, int n_tokens, int heads, int D,
+                                int L, cudaStream_t stream) {
+  const int threads = (D + 31) / 32 * 32;
+  dim3 grid((n_tokens + TG - 1) / TG, heads);
+  const size_t smem = (size_t)TG * L * sizeof(float);
+  if (smem > 48 * 1024) return SI_ERR_TOO_LARGE;
+  SI_LAUNCH((si::delta_prepare_kernel<T, TG>), grid, threads, smem, stream, (const T*)proj, proj_stride,
+            (const T*)w2t, w0, a_bias, prep, n_tokens, heads, D, L);
+  return SI_OK;
+}
+
 SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2t, const float* w0,
                             const float* a_bias, float* prep, int n_tokens, int heads, int D, int L,
                             int dtype, cudaStream_t stream) {
@@ -287,20 +332,18 @@ SI_API int si_delta_prepare(const void* proj, int proj_stride, const void* w2t, 
     return SI_ERR_ARG;
   if (D > 1024 || heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_tokens == 0) return SI_OK;
-  const int threads = (D + 31) / 32 * 32;
-  dim3 grid(n_tokens, heads);
-  const size_t smem = (size_t)L * sizeof(float);
-  if (smem > 48 * 1024) return SI_ERR_TOO_LARGE;
+  const bool many = n_tokens >= 64;
   if (dtype == SI_BF16)
-    SI_LAUNCH(si::delta_prepare_kernel<__nv_bfloat16>, grid, threads, smem, stream,
-              (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)w2t, w0, a_bias, prep,
-              heads, D, L);
-  else if (dtype == SI_F32)
-    SI_LAUNCH(si::delta_prepare_kernel<float>, grid, threads, smem, stream, (const float*)proj,
-              proj_stride, (const float*)w2t, w0, a_bias, prep, heads, D, L);
-  else
-    return SI_ERR_DTYPE;
-  return SI_OK;
+    return many ? launch_delta_prepare<__nv_bfloat16, 8>(proj, proj_stride, w2t, w0, a_bias, prep,
+                                                         n_tokens, heads, D, L, stream)
+                : launch_delta_prepare<__nv_bfloat16, 1>(proj, proj_stride, w2t, w0, a_bias, prep,
+                                                         n_tokens, heads, D, L, stream);
+  if (dtype == SI_F32)
+    return many ? launch_delta_prepare<float, 8>(proj, proj_stride, w2t, w0, a_bias, prep, n_tokens,
+                                                 heads, D, L, stream)
+                : launch_delta_prepare<float, 1>(proj, proj_stride, w2t, w0, a_bias, prep, n_tokens,
+                                                 heads, D, L, stream);
+  return SI_ERR_DTYPE;
 }
 
 template <int R, int KS, bool VEC>

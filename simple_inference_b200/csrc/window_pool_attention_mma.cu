@@ -5,10 +5,13 @@
 // of its warps is one query head of that group, so the group's heads share every key and value
 // the block fetches.  The keys a tile can see are numbered x = 0 .. nb-1 (pooled blocks, nb
 // those seen by the tile's last token) and then the tokens from the first one that the tile's
-// first token sees to the tile's last token; they stream through two shared-memory stages of 64
+// first token sees to the tile's last token; they stream through a ring of shared-memory stages of 64
 // keys (cp.async through the page tables of both caches), and each row masks what it does not
 // see: blocks not yet wholly before ITS window, tokens before its window or after itself.
-// A sequence that brings one token (decoding) is a tile with one row in use.
+// Where a tile's tokens times the group's heads fill no more than the 16 rows of one fragment
+// (a sequence that brings one token: decoding), the rows are (token, head) pairs, every warp
+// holds all of them and takes every n-th run of 16 keys of a stage; the warps' partial results
+// (row maximum, sum and output) are joined through shared memory at the end.
 // The same formulas as the generic kernel (window_pool_attention.cu), which stays the kernel of
 // float32 models and of head sizes that are no multiple of 16 or above 128.
 #include "common.cuh"
@@ -20,8 +23,10 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int WPM_QT = 16;      // query rows of a tile
 constexpr int WPM_KT = 64;      // keys per stage
+constexpr int WPM_NST = 3;      // stages: a tile with few rows spends less on a stage than its copy takes
 constexpr int WPM_PAD = 8;      // elements added to a shared-memory row: no bank conflicts
 constexpr int WPM_MAX_WARPS = 4;
+constexpr int WPM_PAGES = 1024;  // page numbers of a tile kept in shared memory
 
 __device__ __forceinline__ void wpm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -32,6 +37,11 @@ __device__ __forceinline__ void wpm_mma(float (&c)[4], const uint32_t (&a)[4], u
 }
 __device__ __forceinline__ void wpm_ldmatrix_x4_trans(uint32_t (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void wpm_ldmatrix_x4(uint32_t (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
@@ -57,8 +67,8 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   extern __shared__ __align__(16) unsigned char wpm_smem[];
   const int kd = tl.kd, vd = tl.vd, G = tl.kv_heads;
   const int kstride = kd + WPM_PAD, vstride = vd + WPM_PAD;
-  bf16* k_s = reinterpret_cast<bf16*>(wpm_smem);          // [2][KT][kstride]
-  bf16* v_s = k_s + 2 * WPM_KT * kstride;                 // [2][KT][vstride]
+  bf16* k_s = reinterpret_cast<bf16*>(wpm_smem);          // [NST][KT][kstride]
+  bf16* v_s = k_s + WPM_NST * WPM_KT * kstride;           // [NST][KT][vstride]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;                // row and column pair within a fragment
 
@@ -81,9 +91,15 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   }
   if (seq < 0) return;
   const int g = blockIdx.y, Hg = H / G;
-  const int head_in_group = blockIdx.z * (int)(blockDim.x >> 5) + warp;
-  const bool active = head_in_group < Hg;
-  const int h = g * Hg + head_in_group;
+  const int nw = (int)(blockDim.x >> 5);
+  // few rows: all heads of the group in one fragment, the warps share out the keys
+  const bool split = nw > 1 && nq * Hg <= WPM_QT;
+  if (split && blockIdx.z > 0) return;
+  const int head_in_group = blockIdx.z * nw + warp;
+  const bool active = split || head_in_group < Hg;
+  const int n_rows = split ? nq * Hg : nq;
+  auto row_tok = [&](int r) { return split ? r / Hg : r; };          // token of a fragment row
+  auto row_head = [&](int r) { return g * Hg + (split ? r % Hg : head_in_group); };
   const int p0 = positions[t0], p_last = p0 + nq - 1;
   const int lo_min = (W > 0 && p0 - W + 1 > 0) ? p0 - W + 1 : 0;
   const int nb_max = (W > 0 && P > 0 && p_last - W + 1 > 0) ? (p_last - W + 1) / P : 0;
@@ -91,37 +107,63 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   const int n_tiles = (n_slots + WPM_KT - 1) / WPM_KT;
   const int* ttab = tok_table + (size_t)seq * tok_table_stride;
   const int* btab = blk_table ? blk_table + (size_t)seq * blk_table_stride : nullptr;
+  // the page numbers the tile will ask for, side by side in shared memory (a look-up in the
+  // tables themselves would put a trip to memory before every copy): token pages from the
+  // first one seen, then block pages
+  __shared__ int pages_s[WPM_PAGES];
+  const int tp0 = lo_min / tl.rows, n_tp = p_last / tl.rows - tp0 + 1;
+  const int n_bp = nb_max > 0 ? (nb_max - 1) / bl.rows + 1 : 0;
+  const bool staged = n_tp + n_bp <= WPM_PAGES;
+  if (staged) {
+    for (int i = tid; i < n_tp; i += blockDim.x) pages_s[i] = ttab[tp0 + i];
+    for (int i = tid; i < n_bp; i += blockDim.x) pages_s[n_tp + i] = btab[i];
+  }
+  __syncthreads();
   pdl_wait();
 
+  // Eight threads copy one row of a stage (a key and its value, 16 bytes at a time), so a
+  // row's page is looked up once by each of them.
+  const int row_lane = tid >> 3, ch_lane = tid & 7, rows_per_pass = (int)blockDim.x >> 3;
   auto load_tile = [&](int i) {
-    const int st = i & 1;
+    const int st = i % WPM_NST;
     const int kchunks = kd >> 3, per_row = (kd + vd) >> 3;
-    for (int idx = tid; idx < WPM_KT * per_row; idx += blockDim.x) {
-      const int row = idx / per_row, c = idx - row * per_row;
+    for (int row = row_lane; row < WPM_KT; row += rows_per_pass) {
       const int x = i * WPM_KT + row;
-      bf16* dst = c < kchunks ? k_s + (st * WPM_KT + row) * kstride + c * 8
-                              : v_s + (st * WPM_KT + row) * vstride + (c - kchunks) * 8;
+      bf16* kdst = k_s + (st * WPM_KT + row) * kstride;
+      bf16* vdst = v_s + (st * WPM_KT + row) * vstride;
       if (x < n_slots) {
-        const bf16* src;
+        const bf16 *ksrc, *vsrc;
         if (x < nb_max) {
-          const int page = btab[x / bl.rows], r = x % bl.rows;
-          src = c < kchunks ? blk_pool + bl.key_at(page, g, r) + c * 8
-                            : blk_pool + bl.value_at(page, g, r) + (c - kchunks) * 8;
+          const int lp = x / bl.rows, r = x - lp * bl.rows;
+          const int page = staged ? pages_s[n_tp + lp] : btab[lp];
+          ksrc = blk_pool + bl.key_at(page, g, r);
+          vsrc = blk_pool + bl.value_at(page, g, r);
         } else {
           const int j = lo_min + (x - nb_max);
-          const int page = ttab[j / tl.rows], r = j % tl.rows;
-          src = c < kchunks ? tok_pool + tl.key_at(page, g, r) + c * 8
-                            : tok_pool + tl.value_at(page, g, r) + (c - kchunks) * 8;
+          const int lp = j / tl.rows, r = j - lp * tl.rows;
+          const int page = staged ? pages_s[lp - tp0] : ttab[lp];
+          ksrc = tok_pool + tl.key_at(page, g, r);
+          vsrc = tok_pool + tl.value_at(page, g, r);
         }
-        wpm_cp16(dst, src);
+        for (int c = ch_lane; c < per_row; c += 8) {
+          if (c < kchunks) wpm_cp16(kdst + c * 8, ksrc + c * 8);
+          else wpm_cp16(vdst + (c - kchunks) * 8, vsrc + (c - kchunks) * 8);
+        }
       } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // a value row must not be garbage
+        for (int c = ch_lane; c < per_row; c += 8) {   // a value row must not be garbage
+          if (c < kchunks) *reinterpret_cast<uint4*>(kdst + c * 8) = make_uint4(0, 0, 0, 0);
+          else *reinterpret_cast<uint4*>(vdst + (c - kchunks) * 8) = make_uint4(0, 0, 0, 0);
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  load_tile(0);
+#pragma unroll
+  for (int i = 0; i < WPM_NST - 1; ++i) {
+    if (i < n_tiles) load_tile(i);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
 
   // this warp's queries as A fragments: rows gq and gq+8 of the tile, all of the head's columns
   uint32_t qf[KD16][4];
@@ -131,8 +173,9 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
     for (int e = 0; e < 4; ++e) {
       const int row = gq + (e & 1) * 8, col = kk * 16 + tq * 2 + (e >> 1) * 8;
       uint32_t v = 0;
-      if (active && row < nq && col < kd)
-        v = *reinterpret_cast<const uint32_t*>(q + (size_t)(t0 + row) * q_stride + (size_t)h * kd + col);
+      if (active && row < n_rows && col < kd)
+        v = *reinterpret_cast<const uint32_t*>(q + (size_t)(t0 + row_tok(row)) * q_stride +
+                                               (size_t)row_head(row) * kd + col);
       qf[kk][e] = v;
     }
   }
@@ -140,9 +183,17 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   int p_row[2], nb_row[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    p_row[r] = p0 + gq + r * 8;
+    p_row[r] = p0 + row_tok(gq + r * 8);
     nb_row[r] = (W > 0 && P > 0 && p_row[r] - W + 1 > 0) ? (p_row[r] - W + 1) / P : 0;
   }
+  // which runs of 16 keys of a stage are this warp's (all of them unless the warps share them out)
+  unsigned own = 0;
+#pragma unroll
+  for (int kk = 0; kk < WPM_KT / 16; ++kk)
+    if (!split || kk % nw == warp) own |= 1u << kk;
+  // a stage needs no masking when every row sees all of it: its blocks are seen by the first
+  // token already, its tokens lie inside the last token's window and not after the first token
+  const int nb_first = (W > 0 && P > 0 && p0 - W + 1 > 0) ? (p0 - W + 1) / P : 0;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   float o[VD8][4];
 #pragma unroll
@@ -151,42 +202,56 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
     for (int e = 0; e < 4; ++e) o[n][e] = 0.0f;
 
   for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) load_tile(i + 1);
+    if (i + WPM_NST - 1 < n_tiles) load_tile(i + WPM_NST - 1);   // into the stage tile i-1 has left
     else asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(WPM_NST - 1) : "memory");
     __syncthreads();
     if (active) {
-      const bf16* ks = k_s + (i & 1) * WPM_KT * kstride;
-      const bf16* vs = v_s + (i & 1) * WPM_KT * vstride;
+      const bf16* ks = k_s + (i % WPM_NST) * WPM_KT * kstride;
+      const bf16* vs = v_s + (i % WPM_NST) * WPM_KT * vstride;
       float s[WPM_KT / 8][4];
+      const unsigned k_base = (unsigned)__cvta_generic_to_shared(ks);
 #pragma unroll
-      for (int nt = 0; nt < WPM_KT / 8; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+      for (int nt = 0; nt < WPM_KT / 8; nt += 2) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = s[nt + 1][e] = 0.0f;
+        if (!((own >> (nt >> 1)) & 1)) continue;   // another warp's run of 16 keys
 #pragma unroll
         for (int kk = 0; kk < KD16; ++kk) {
           if (kk * 16 < kd) {
-            const bf16* kp = ks + (nt * 8 + gq) * kstride + kk * 16 + tq * 2;
-            wpm_mma(s[nt], qf[kk], *reinterpret_cast<const uint32_t*>(kp),
-                    *reinterpret_cast<const uint32_t*>(kp + 8));
+            // four 8x8 pieces: keys nt*8.. and (nt+1)*8.., each with the step's two halves
+            const int key = (nt + (lane >> 4)) * 8 + (lane & 7);
+            uint32_t b[4];
+            wpm_ldmatrix_x4(b, k_base + (unsigned)((key * kstride + kk * 16 + ((lane >> 3) & 1) * 8) * 2));
+            wpm_mma(s[nt], qf[kk], b[0], b[1]);
+            wpm_mma(s[nt + 1], qf[kk], b[2], b[3]);
           }
         }
       }
       // scale and mask; row maxima
       float mx[2] = {-INFINITY, -INFINITY};
+      const int x0 = i * WPM_KT, x1 = x0 + WPM_KT - 1;   // the stage's first and last slot
+      bool all_seen = x1 < n_slots;   // (rows past the tile's last are never stored)
+      if (x0 < nb_max) all_seen = all_seen && x1 < nb_first;
+      else all_seen = all_seen && lo_min + (x1 - nb_max) <= p0 &&
+                      (W <= 0 || lo_min + (x0 - nb_max) > p_last - W);
 #pragma unroll
       for (int nt = 0; nt < WPM_KT / 8; ++nt) {
+        if (!((own >> (nt >> 1)) & 1)) continue;   // not this warp's keys: neither masked nor summed
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          const int x = i * WPM_KT + nt * 8 + tq * 2 + (e & 1);
-          bool vis;
-          if (x < nb_max) {
-            vis = x < nb_row[r];
-          } else {
-            const int j = lo_min + (x - nb_max);
-            vis = j <= p_row[r] && (W <= 0 || j > p_row[r] - W);
+          bool vis = true;
+          if (!all_seen) {
+            const int x = x0 + nt * 8 + tq * 2 + (e & 1);
+            if (x < nb_max) {
+              vis = vis && x < nb_row[r];
+            } else {
+              const int j = lo_min + (x - nb_max);
+              vis = vis && j <= p_row[r] && (W <= 0 || j > p_row[r] - W);
+            }
+            vis = vis && x < n_slots && gq + r * 8 < n_rows;
           }
-          vis = vis && x < n_slots && gq + r * 8 < nq;
           const float v = vis ? s[nt][e] * scale : -INFINITY;
           s[nt][e] = v;
           mx[r] = fmaxf(mx[r], v);
@@ -210,6 +275,7 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
       }
 #pragma unroll
       for (int nt = 0; nt < WPM_KT / 8; ++nt) {
+        if (!((own >> (nt >> 1)) & 1)) continue;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float pv = __expf(s[nt][e] - m_use[e >> 1]);
@@ -220,6 +286,7 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
       // O += P V, 16 keys at a time; V fragments come transposed out of shared memory
 #pragma unroll
       for (int kk = 0; kk < WPM_KT / 16; ++kk) {
+        if (!((own >> kk) & 1)) continue;
         uint32_t pa[4];
         pa[0] = wpm_pack(s[2 * kk][0], s[2 * kk][1]);
         pa[1] = wpm_pack(s[2 * kk][2], s[2 * kk][3]);
@@ -243,40 +310,93 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   pdl_trigger();
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-  // normalise, hand the tile to shared memory, turn every head's rows back by their
-  // positions and store
-  float* o_s = reinterpret_cast<float*>(wpm_smem) + warp * WPM_QT * vd;   // [16][vd] of this warp
-  if (active) {
+  float* smem_f = reinterpret_cast<float*>(wpm_smem);
+  const int vhalf = vd >> 1;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  if (!split) {
+    // normalise, hand the warp's rows to shared memory, turn them back by their positions, store
+    float* o_s = smem_f + warp * WPM_QT * vd;   // [16][vd] of this warp
+    if (active) {
+      const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+#pragma unroll
+      for (int n = 0; n < VD8; ++n) {
+        if (n * 8 < vd) {
+          const int col = n * 8 + tq * 2;
+          o_s[gq * vd + col] = o[n][0] * inv0;
+          o_s[gq * vd + col + 1] = o[n][1] * inv0;
+          o_s[(gq + 8) * vd + col] = o[n][2] * inv1;
+          o_s[(gq + 8) * vd + col + 1] = o[n][3] * inv1;
+        }
+      }
+      __syncwarp();
+      const int h = row_head(0);
+      for (int idx = lane; idx < nq * vd; idx += 32) {
+        const int row = idx / vd, d = idx - row * vd;
+        float x = o_s[idx];
+        if (freq_v) {
+          const int fi = d < vhalf ? d : d - vhalf;
+          float sn, cs;
+          sincosf((float)(p0 + row) * freq_v[fi], &sn, &cs);
+          const float y = o_s[row * vd + (d < vhalf ? d + vhalf : d - vhalf)];
+          x = d < vhalf ? x * cs + y * sn : x * cs - y * sn;
+        }
+        out[(size_t)(t0 + row) * out_stride + (size_t)h * vd + d] = __float2bfloat16_rn(x);
+      }
+    }
+    return;
+  }
+  // the warps' partial results side by side, then one pass that joins them, one that turns
+  float* o_w = smem_f + warp * WPM_QT * vd;              // [nw][16][vd] unnormalised sums
+  float* ml_s = smem_f + nw * WPM_QT * vd;               // [nw][16][2] row maximum and sum
+  float* fin = ml_s + nw * WPM_QT * 2;                   // [16][vd] joined rows
+#pragma unroll
+  for (int n = 0; n < VD8; ++n) {
+    if (n * 8 < vd) {
+      const int col = n * 8 + tq * 2;
+      o_w[gq * vd + col] = o[n][0];
+      o_w[gq * vd + col + 1] = o[n][1];
+      o_w[(gq + 8) * vd + col] = o[n][2];
+      o_w[(gq + 8) * vd + col + 1] = o[n][3];
+    }
+  }
+  if (tq == 0) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      ml_s[(warp * WPM_QT + gq + r * 8) * 2] = m_run[r];
+      ml_s[(warp * WPM_QT + gq + r * 8) * 2 + 1] = l_run[r];
     }
-    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
-#pragma unroll
-    for (int n = 0; n < VD8; ++n) {
-      if (n * 8 < vd) {
-        const int col = n * 8 + tq * 2;
-        o_s[gq * vd + col] = o[n][0] * inv0;
-        o_s[gq * vd + col + 1] = o[n][1] * inv0;
-        o_s[(gq + 8) * vd + col] = o[n][2] * inv1;
-        o_s[(gq + 8) * vd + col + 1] = o[n][3] * inv1;
-      }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_rows * vd; idx += blockDim.x) {
+    const int row = idx / vd, d = idx - row * vd;
+    float m_all = -INFINITY;
+    for (int w = 0; w < nw; ++w) m_all = fmaxf(m_all, ml_s[(w * WPM_QT + row) * 2]);
+    float l_all = 0.0f, acc = 0.0f;
+    for (int w = 0; w < nw; ++w) {   // fixed order
+      const float m_w = ml_s[(w * WPM_QT + row) * 2];
+      const float f = m_w == -INFINITY ? 0.0f : __expf(m_w - m_all);
+      l_all = fmaf(ml_s[(w * WPM_QT + row) * 2 + 1], f, l_all);
+      acc = fmaf(smem_f[(w * WPM_QT + row) * vd + d], f, acc);
     }
-    __syncwarp();
-    const int vhalf = vd >> 1;
-    for (int idx = lane; idx < nq * vd; idx += 32) {
-      const int row = idx / vd, d = idx - row * vd;
-      float x = o_s[idx];
-      if (freq_v) {
-        const int fi = d < vhalf ? d : d - vhalf;
-        float sn, cs;
-        sincosf((float)(p0 + row) * freq_v[fi], &sn, &cs);
-        const float y = o_s[row * vd + (d < vhalf ? d + vhalf : d - vhalf)];
-        x = d < vhalf ? x * cs + y * sn : x * cs - y * sn;
-      }
-      out[(size_t)(t0 + row) * out_stride + (size_t)h * vd + d] = __float2bfloat16_rn(x);
+    fin[idx] = acc / l_all;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_rows * vd; idx += blockDim.x) {
+    const int row = idx / vd, d = idx - row * vd;
+    const int tok = row_tok(row);
+    float x = fin[idx];
+    if (freq_v) {
+      const int fi = d < vhalf ? d : d - vhalf;
+      float sn, cs;
+      sincosf((float)(p0 + tok) * freq_v[fi], &sn, &cs);
+      const float y = fin[row * vd + (d < vhalf ? d + vhalf : d - vhalf)];
+      x = d < vhalf ? x * cs + y * sn : x * cs - y * sn;
     }
+    out[(size_t)(t0 + tok) * out_stride + (size_t)row_head(row) * vd + d] = __float2bfloat16_rn(x);
   }
 }
 
@@ -291,7 +411,10 @@ static int launch_wp_attention_mma(const void* q, int q_stride, const int* posit
                                    int P, const float* freq_v, cudaStream_t stream) {
   const int Hg = H / tl.kv_heads;
   const int warps = Hg < si::WPM_MAX_WARPS ? Hg : si::WPM_MAX_WARPS;
-  const size_t smem = (size_t)2 * si::WPM_KT * (tl.kd + tl.vd + 2 * si::WPM_PAD) * sizeof(si::bf16);
+  const size_t stages = (size_t)si::WPM_NST * si::WPM_KT * (tl.kd + tl.vd + 2 * si::WPM_PAD) * sizeof(si::bf16);
+  // joining the warps' partial results reuses the stages' memory and may need a little more
+  const size_t join = (size_t)((warps + 1) * si::WPM_QT * tl.vd + warps * si::WPM_QT * 2) * sizeof(float);
+  const size_t smem = stages > join ? stages : join;
   auto kern = si::wp_attention_mma_kernel<KD16, VD8>;
   if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
   // an upper bound of the tiles: every sequence's last tile may be short
