@@ -60,7 +60,7 @@ constexpr bool SK_EARLY_TRIGGER = true;
 constexpr int SK_RING_BYTES = SK_WARPS * SK_STAGES * SK_STAGE_BYTES;
 constexpr int SK_MAX_SPLITS = 8;
 
-enum SkinnyEpilogue { SK_BF16 = 0, SK_F32 = 1, SK_SWIGLU = 2, SK_ROPE = 3, SK_PARTIAL = 4 };
+enum SkinnyEpilogue { SK_BF16 = 0, SK_F32 = 1, SK_SWIGLU = 2, SK_ROPE = 3, SK_PARTIAL = 4, SK_RELU2 = 5 };
 
 // What the rotary epilogue needs beside the product: see rope_kv.cu for the meanings.
 struct RopeEpilogue {
@@ -318,7 +318,10 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) s += rd[w][r][m];
-        if (EPI == SK_BF16) {
+        if (EPI == SK_RELU2) {   // squared ReLU
+          const float a = fmaxf(s, 0.0f);
+          reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(a * a);
+        } else if (EPI == SK_BF16) {
           reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(s);
         } else if (EPI == SK_F32) {
           reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = s;
@@ -414,11 +417,13 @@ SI_API int si_gemm_skinny_bf16(const void* X, int ldx, const void* W, void* out,
     if (epilogue == SK_BF16) return launch_skinny<1, SK_BF16>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_F32) return launch_skinny<1, SK_F32>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_SWIGLU) return launch_skinny<1, SK_SWIGLU>(X, ldx, W, out, ldo, M, N, K, 1, stream);
+    if (epilogue == SK_RELU2) return launch_skinny<1, SK_RELU2>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_PARTIAL) return launch_skinny<1, SK_PARTIAL>(X, ldx, W, out, ldo, M, N, K, splits, stream);
   } else {
     if (epilogue == SK_BF16) return launch_skinny<2, SK_BF16>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_F32) return launch_skinny<2, SK_F32>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_SWIGLU) return launch_skinny<2, SK_SWIGLU>(X, ldx, W, out, ldo, M, N, K, 1, stream);
+    if (epilogue == SK_RELU2) return launch_skinny<2, SK_RELU2>(X, ldx, W, out, ldo, M, N, K, 1, stream);
     if (epilogue == SK_PARTIAL) return launch_skinny<2, SK_PARTIAL>(X, ldx, W, out, ldo, M, N, K, splits, stream);
   }
   return SI_ERR_ARG;

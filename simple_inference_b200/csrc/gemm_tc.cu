@@ -44,7 +44,7 @@ constexpr uint32_t TC_TMEM_COLS = 512;                   // two accumulators of 
 constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 
 enum TcStatus { TC_OK = 0, TC_TIMEOUT_PRODUCER = 1, TC_TIMEOUT_MMA = 2, TC_TIMEOUT_EPILOGUE = 3 };
-enum TcEpilogue { TC_EPI_BF16 = 0, TC_EPI_SWIGLU = 2 };
+enum TcEpilogue { TC_EPI_BF16 = 0, TC_EPI_SWIGLU = 2, TC_EPI_RELU2 = 5 };  // 5: plain output, max(x,0)^2
 
 // ------------------------------------------------------------------ PTX helpers
 // (mbarrier and TMA helpers are in tma.cuh)
@@ -202,8 +202,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               if (col < n_out) {
                 float w8[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < 8; ++i) {
                   w8[i] = __uint_as_float(j < 2 ? a[j * 8 + i] : b[(j - 2) * 8 + i]);
+                  if (up_row0) w8[i] = fmaxf(w8[i], 0.0f) * fmaxf(w8[i], 0.0f);   // squared ReLU
+                }
                 store8<bf16>(orow + c * 32 + j * 8, w8);
               }
             }
@@ -221,7 +223,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               if (col < n_out) {
                 float w8[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) w8[i] = __uint_as_float(a[j * 8 + i]);
+                for (int i = 0; i < 8; ++i) {
+                  w8[i] = __uint_as_float(a[j * 8 + i]);
+                  if (up_row0) w8[i] = fmaxf(w8[i], 0.0f) * fmaxf(w8[i], 0.0f);
+                }
                 store8<bf16>(orow + c0 + j * 8, w8);
               }
             }
@@ -286,7 +291,7 @@ static int launch_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* o
 }  // namespace si
 
 // out[M, N] = X[M, K] W[N, K]^T in bfloat16 (epilogue 0), or out[M, N] = silu(X Wg^T) * (X Wu^T)
-// with W = [Wg; Wu] of 2N rows (epilogue 2).  K and N multiples of 8, ldx and ldo multiples of 8,
+// with W = [Wg; Wu] of 2N rows (epilogue 2), or out = max(X W^T, 0)^2 (epilogue 5).  K and N multiples of 8, ldx and ldo multiples of 8,
 // all pointers 16-byte aligned.  status: one int in device memory, 0 while all is well.
 SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N,
                            int K, int epilogue, int* status, cudaStream_t stream) {
@@ -295,7 +300,8 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
     return SI_ERR_ARG;
   if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return SI_ERR_UNSUPPORTED;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)out) & 15) return SI_ERR_ARG;
-  if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_SWIGLU) return SI_ERR_ARG;
+  if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_SWIGLU && epilogue != TC_EPI_RELU2) return SI_ERR_ARG;
+  const int act = epilogue == TC_EPI_RELU2 ? 1 : 0;   // rides in the plain epilogue's unused up_row0
   if (M == 0) return SI_OK;
   static int n_sms = 0;
   if (n_sms == 0) {
@@ -315,7 +321,7 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
   if (!make_map(&map_w, W, N, K, K, bn)) return SI_ERR_UNSUPPORTED;
 #define SI_TC_CASE(W)                                                                         \
   case W:                                                                                     \
-    return launch_tc<TC_EPI_BF16, W>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, \
+    return launch_tc<TC_EPI_BF16, W>(map_x, map_w, (bf16*)out, ldo, M, N, K, act, status, n_sms, \
                                      stream)
   switch (bn) {
     SI_TC_CASE(256);
@@ -327,7 +333,7 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
     SI_TC_CASE(160);
     SI_TC_CASE(144);
     default:
-      return launch_tc<TC_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms,
+      return launch_tc<TC_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, act, status, n_sms,
                                          stream);
   }
 #undef SI_TC_CASE

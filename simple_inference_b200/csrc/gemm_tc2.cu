@@ -44,7 +44,7 @@ constexpr uint32_t T2_STAGE_BYTES = T2_SUB * T2_SUB_BYTES;
 constexpr uint32_t T2_TMEM_COLS = 512;
 constexpr uint32_t T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
 
-enum { T2_EPI_BF16 = 0, T2_EPI_SWIGLU = 2, T2_EPI_PARTIAL = 4 };
+enum { T2_EPI_BF16 = 0, T2_EPI_SWIGLU = 2, T2_EPI_RELU2 = 5, T2_EPI_PARTIAL = 4 };
 constexpr int T2_MAX_SPLITS = 8;
 enum { T2_TIMEOUT_PRODUCER = 1, T2_TIMEOUT_MMA = 2, T2_TIMEOUT_EPILOGUE = 3 };
 
@@ -288,8 +288,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
               if (col < n_out) {
                 float w8[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < 8; ++i) {
                   w8[i] = __uint_as_float(j < 2 ? a[j * 8 + i] : b[(j - 2) * 8 + i]);
+                  if (up_row0) w8[i] = fmaxf(w8[i], 0.0f) * fmaxf(w8[i], 0.0f);   // squared ReLU
+                }
                 store8<bf16>(orow + c * 32 + j * 8, w8);
               }
             }
@@ -307,7 +309,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
               if (col < n_out) {
                 float w8[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) w8[i] = __uint_as_float(a[j * 8 + i]);
+                for (int i = 0; i < 8; ++i) {
+                  w8[i] = __uint_as_float(a[j * 8 + i]);
+                  if (up_row0) w8[i] = fmaxf(w8[i], 0.0f) * fmaxf(w8[i], 0.0f);
+                }
                 store8<bf16>(orow + c0 + j * 8, w8);
               }
             }
@@ -394,7 +399,8 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
     return SI_ERR_ARG;
   if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return SI_ERR_UNSUPPORTED;
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)out) & 15) return SI_ERR_ARG;
-  if (epilogue != T2_EPI_BF16 && epilogue != T2_EPI_SWIGLU) return SI_ERR_ARG;
+  if (epilogue != T2_EPI_BF16 && epilogue != T2_EPI_SWIGLU && epilogue != T2_EPI_RELU2) return SI_ERR_ARG;
+  const int act = epilogue == T2_EPI_RELU2 ? 1 : 0;   // rides in the plain epilogue's unused up_row0
   if (M == 0) return SI_OK;
   static int n_sms = 0;
   if (n_sms == 0) {
@@ -415,7 +421,7 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
   if (!make_bf16_map(&map_w, W, N, K, K, bn / 2)) return SI_ERR_UNSUPPORTED;
 #define SI_T2_CASE(W)                                                                          \
   case W:                                                                                      \
-    return launch_tc2<T2_EPI_BF16, W>(map_x, map_w, out, ldo, M, N, K, 0, 1, status, n_sms, \
+    return launch_tc2<T2_EPI_BF16, W>(map_x, map_w, out, ldo, M, N, K, act, 1, status, n_sms, \
                                       stream)
   switch (bn) {
     SI_T2_CASE(256);
@@ -427,7 +433,7 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
     SI_T2_CASE(160);
     SI_T2_CASE(144);
     default:
-      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, out, ldo, M, N, K, 0, 1, status, n_sms,
+      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, out, ldo, M, N, K, act, 1, status, n_sms,
                                           stream);
   }
 #undef SI_T2_CASE

@@ -294,8 +294,9 @@ PAIRED_MIN_ROWS = 256  # from this many rows a tile of 256 rows on a pair of SMs
 
 
 def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
-              paired: bool | None = None) -> torch.Tensor:
-    """The tcgen05 product: ``out = x @ weight.T`` (bfloat16), or its SwiGLU form.
+              paired: bool | None = None, relu2: bool = False) -> torch.Tensor:
+    """The tcgen05 product: ``out = x @ weight.T`` (bfloat16), its SwiGLU form, or (``relu2``)
+    ``out = max(x @ weight.T, 0)^2``.
 
     ``paired``: run on pairs of SMs (256-row tiles); by default from 256 rows on."""
     _dev(x, weight, out)
@@ -308,7 +309,7 @@ def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: 
         paired = m >= PAIRED_MIN_ROWS
     fn = core().si_gemm_tc2_bf16 if paired else core().si_gemm_tc_bf16
     _check(fn(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), m, n, k,
-              2 if swiglu else 0, _p(status_tensor(x.device)), _stream()),
+              2 if swiglu else (5 if relu2 else 0), _p(status_tensor(x.device)), _stream()),
            "gemm_tc2" if paired else "gemm_tc")
     return out
 
@@ -348,6 +349,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
         torch.mm(x, weight.t(), out=out)
     else:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    return out
+
+
+def linear_relu2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = max(x @ weight.T, 0)^2``: in bfloat16 the square of the rectifier is the epilogue
+    of the product kernels (few rows: weight-streaming kernel; 96 rows and more: tcgen05);
+    float32 models and the row counts in between run the product and then ``relu2``."""
+    _dev(x, weight, out)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or out.shape != (m, n) or x.dtype != weight.dtype or out.dtype != x.dtype:
+        raise KernelError("linear_relu2: shapes or dtypes do not fit")
+    if x.dtype == torch.bfloat16 and _skinny_ok(x, weight):
+        _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0),
+                                          m, n, k, 5, _stream()), "gemm_skinny_relu2")
+    elif x.dtype == torch.bfloat16 and _tc_ok(x, weight, n) and out.stride(0) % 8 == 0:
+        linear_tc(x, weight, out, relu2=True)
+    else:
+        linear(x, weight, out)
+        relu2(out, out)
     return out
 
 
@@ -790,7 +811,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     return out
 
 
-__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_tc",
+__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_relu2", "linear_tc",
            "linear_for_residual", "PartialSums",
            "can_fuse_swiglu", "check_status", "status_tensor",
            "rope_kv_store", "can_fuse_projection_rope", "linear_rope_kv_store", "attention_generic", "paged_attention", "attention_prefill_wide", "wide_prefill_fits", "plan_kv_splits", "sample", "core", "attention_library"]

@@ -52,8 +52,8 @@ class SwiGLU(FeedForward):
 
 @register_feed_forward("relu2")
 class SquaredReLU(FeedForward):
-    """``y = W_down relu(W_up x)^2``: two matrices, the square of the rectifier between them
-    (float32 arithmetic, one rounding)."""
+    """``y = W_down relu(W_up x)^2``: two matrices, the square of the rectifier between them,
+    formed on the first product's float32 sums before their one rounding."""
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = int(hidden_size)
@@ -75,7 +75,6 @@ class SquaredReLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
         hidden = ctx.ws.get("mlp.hidden", (n, self.intermediate_size), x.dtype)
-        ops.linear(x, self.w_up, hidden)
-        ops.relu2(hidden, hidden)
+        ops.linear_relu2(x, self.w_up, hidden)   # the activation is the product's epilogue
         return ops.linear_for_residual(hidden, self.w_down, ctx.ws, "mlp.down",
                                        getattr(ctx, "partial_sums_ok", False))

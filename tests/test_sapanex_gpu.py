@@ -276,3 +276,18 @@ def test_tensor_core_attention_equals_the_generic_kernel(H, G, kd, vd, W, P):
     assert torch.isfinite(fast).all() and generic.abs().max() < 100   # nobody read a poisoned page
     assert (fast - generic).abs().max() < 0.04 * generic.abs().max()
     assert relative_error(fast, generic) < 0.03
+
+
+@pytest.mark.parametrize("rows", [1, 9, 16, 40, 130, 300])
+def test_squared_relu_as_the_epilogue_of_the_product(rows):
+    from simple_inference_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, 192, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(328, 192, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    out = ops.linear_relu2(x, w, torch.empty(rows, 328, dtype=torch.bfloat16, device="cuda"))
+    ops.check_status(x.device)
+    want = torch.relu(x.float() @ w.float().T) ** 2
+    assert (out.float() - want).abs().max() <= 0.01 * want.abs().max() + 1e-3
+    x32, w32 = x.float(), w.float()
+    out32 = ops.linear_relu2(x32, w32, torch.empty(rows, 328, device="cuda"))
+    assert torch.allclose(out32, want, rtol=1e-5, atol=1e-5)
