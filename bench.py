@@ -511,11 +511,16 @@ def run_sapanex(args) -> int:
     import torch
     from simple_inference_b200.models.load import random_model
     out = {"only": "sapanex", "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT,
-           "layers": SAPANEX_LAYERS, "window": SAPANEX_WINDOW, "pool": SAPANEX_POOL, "shapes": {}}
+           "layers": args.layers or SAPANEX_LAYERS, "window": SAPANEX_WINDOW, "pool": SAPANEX_POOL, "shapes": {}}
     shapes = [args.shape] if args.shape in SAPANEX_SHAPES and args.shape_given else list(SAPANEX_SHAPES)
     for shape in shapes:
         row = {}
         for name, config in (("sapanex", sapanex_config(shape)), ("llama", llama_like(shape))):
+            if args.layers:   # fewer layers (for profiles): the first ones of either model
+                if name == "sapanex":
+                    config["layers"] = config["layers"][:args.layers]
+                else:
+                    config["num_hidden_layers"] = args.layers
             cfg, model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             pre_ms = time_prefill(model, cfg, reps=3)
             entry = {"prefill_ms": round(pre_ms, 3),

@@ -291,23 +291,35 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
   }
 }
 
+// One block per token; a warp takes heads in turn: the head's mean square over its D channels is
+// a sum within the warp, in a fixed order.
+constexpr int DELTA_OUT_WARPS = 8;
+
 template <typename T, typename TW>
-__global__ void delta_output_kernel(const float* __restrict__ o, const T* __restrict__ proj,
-                                    int proj_stride, const TW* __restrict__ gain, T* __restrict__ out,
-                                    int heads, int D, float eps) {
-  __shared__ float red[32];
-  const int t = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+__global__ void __launch_bounds__(32 * DELTA_OUT_WARPS)
+delta_output_kernel(const float* __restrict__ o, const T* __restrict__ proj, int proj_stride,
+                    const TW* __restrict__ gain, T* __restrict__ out, int heads, int D, float eps) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int HD = heads * D;
-  const bool mine = c < D;
-  const int col = h * D + c;
-  const float gn = mine ? to_f32<TW>(gain[col]) : 0.0f;
   pdl_wait();
   pdl_trigger();
-  const float x = mine ? o[(size_t)t * HD + col] : 0.0f;
-  const float ss = block_sum(x * x, red);
-  if (!mine) return;
-  const float g = sigmoidf_(to_f32<T>(proj[(size_t)t * proj_stride + 3 * HD + col]));
-  out[(size_t)t * HD + col] = from_f32<T>(x / sqrtf(ss / (float)D + eps) * gn * g);
+  const float* orow = o + (size_t)t * HD;
+  const T* grow = proj + (size_t)t * proj_stride + 3 * HD;
+  T* yrow = out + (size_t)t * HD;
+  for (int h = warp; h < heads; h += DELTA_OUT_WARPS) {
+    float ss = 0.0f;
+    for (int c = lane; c < D; c += 32) {
+      const float x = orow[h * D + c];
+      ss = fmaf(x, x, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int c = lane; c < D; c += 32) {
+      const int col = h * D + c;
+      const float g = sigmoidf_(to_f32<T>(grow[col]));
+      yrow[col] = from_f32<T>(orow[col] * inv * to_f32<TW>(gain[col]) * g);
+    }
+  }
 }
 
 }  // namespace si
@@ -389,20 +401,18 @@ SI_API int si_delta_output(const float* o, const void* proj, int proj_stride, co
                            int gain_dtype, cudaStream_t stream) {
   if (!o || !proj || !gain || !out || n_tokens < 0 || heads <= 0 || D <= 0 || !(eps > 0.0f))
     return SI_ERR_ARG;
-  if (D > 1024 || heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_tokens == 0) return SI_OK;
-  const int threads = (D + 31) / 32 * 32;
-  dim3 grid(n_tokens, heads);
+  const int threads = 32 * si::DELTA_OUT_WARPS;
   if (dtype == SI_BF16 && gain_dtype == SI_BF16)
-    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, __nv_bfloat16>), grid, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, threads, 0, stream, o,
               (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)gain, (__nv_bfloat16*)out,
               heads, D, eps);
   else if (dtype == SI_BF16 && gain_dtype == SI_F32)
-    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, float>), grid, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, float>), n_tokens, threads, 0, stream, o,
               (const __nv_bfloat16*)proj, proj_stride, (const float*)gain, (__nv_bfloat16*)out, heads,
               D, eps);
   else if (dtype == SI_F32 && gain_dtype == SI_F32)
-    SI_LAUNCH((si::delta_output_kernel<float, float>), grid, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<float, float>), n_tokens, threads, 0, stream, o,
               (const float*)proj, proj_stride, (const float*)gain, (float*)out, heads, D, eps);
   else
     return SI_ERR_DTYPE;

@@ -11,7 +11,10 @@
 // Where a tile's tokens times the group's heads fill no more than the 16 rows of one fragment
 // (a sequence that brings one token: decoding), the rows are (token, head) pairs, every warp
 // holds all of them and takes every n-th run of 16 keys of a stage; the warps' partial results
-// (row maximum, sum and output) are joined through shared memory at the end.
+// (row maximum, sum and output) are joined through shared memory at the end.  Such tiles can also
+// be shared out among several blocks (every n-th stage each) that leave their partial results in
+// scratch memory for a small second kernel to join: a decode step has too few (request, key/value
+// head) pairs to fill the GPU otherwise.
 // The same formulas as the generic kernel (window_pool_attention.cu), which stays the kernel of
 // float32 models and of head sizes that are no multiple of 16 or above 128.
 #include "common.cuh"
@@ -63,7 +66,8 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
                         const int* __restrict__ tok_table, int tok_table_stride, PlanesLayout tl,
                         const bf16* __restrict__ blk_pool, const int* __restrict__ blk_table,
                         int blk_table_stride, PlanesLayout bl, bf16* __restrict__ out, int out_stride,
-                        int H, float scale, int W, int P, const float* __restrict__ freq_v) {
+                        int H, float scale, int W, int P, const float* __restrict__ freq_v,
+                        int key_splits, float* __restrict__ scratch) {
   extern __shared__ __align__(16) unsigned char wpm_smem[];
   const int kd = tl.kd, vd = tl.vd, G = tl.kv_heads;
   const int kstride = kd + WPM_PAD, vstride = vd + WPM_PAD;
@@ -94,7 +98,8 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   const int nw = (int)(blockDim.x >> 5);
   // few rows: all heads of the group in one fragment, the warps share out the keys
   const bool split = nw > 1 && nq * Hg <= WPM_QT;
-  if (split && blockIdx.z > 0) return;
+  const int Z = split ? key_splits : 1, zi = split ? (int)blockIdx.z : 0;   // blocks that share the stages
+  if (split ? (int)blockIdx.z >= Z : (int)blockIdx.z * nw >= Hg) return;
   const int head_in_group = blockIdx.z * nw + warp;
   const bool active = split || head_in_group < Hg;
   const int n_rows = split ? nq * Hg : nq;
@@ -104,7 +109,8 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   const int lo_min = (W > 0 && p0 - W + 1 > 0) ? p0 - W + 1 : 0;
   const int nb_max = (W > 0 && P > 0 && p_last - W + 1 > 0) ? (p_last - W + 1) / P : 0;
   const int n_slots = nb_max + (p_last - lo_min + 1);
-  const int n_tiles = (n_slots + WPM_KT - 1) / WPM_KT;
+  const int all_tiles = (n_slots + WPM_KT - 1) / WPM_KT;
+  const int n_tiles = zi < all_tiles ? (all_tiles - zi + Z - 1) / Z : 0;   // this block's: zi, zi+Z, ...
   const int* ttab = tok_table + (size_t)seq * tok_table_stride;
   const int* btab = blk_table ? blk_table + (size_t)seq * blk_table_stride : nullptr;
   // the page numbers the tile will ask for, side by side in shared memory (a look-up in the
@@ -124,8 +130,9 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   // Eight threads copy one row of a stage (a key and its value, 16 bytes at a time), so a
   // row's page is looked up once by each of them.
   const int row_lane = tid >> 3, ch_lane = tid & 7, rows_per_pass = (int)blockDim.x >> 3;
-  auto load_tile = [&](int i) {
-    const int st = i % WPM_NST;
+  auto load_tile = [&](int own_i) {   // the block's own_i-th stage of keys
+    const int st = own_i % WPM_NST;
+    const int i = zi + own_i * Z;
     const int kchunks = kd >> 3, per_row = (kd + vd) >> 3;
     for (int row = row_lane; row < WPM_KT; row += rows_per_pass) {
       const int x = i * WPM_KT + row;
@@ -230,7 +237,7 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
       }
       // scale and mask; row maxima
       float mx[2] = {-INFINITY, -INFINITY};
-      const int x0 = i * WPM_KT, x1 = x0 + WPM_KT - 1;   // the stage's first and last slot
+      const int x0 = (zi + i * Z) * WPM_KT, x1 = x0 + WPM_KT - 1;   // the stage's first and last slot
       bool all_seen = x1 < n_slots;   // (rows past the tile's last are never stored)
       if (x0 < nb_max) all_seen = all_seen && x1 < nb_first;
       else all_seen = all_seen && lo_min + (x1 - nb_max) <= p0 &&
@@ -382,8 +389,18 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
       l_all = fmaf(ml_s[(w * WPM_QT + row) * 2 + 1], f, l_all);
       acc = fmaf(smem_f[(w * WPM_QT + row) * vd + d], f, acc);
     }
-    fin[idx] = acc / l_all;
+    if (Z > 1) {   // unnormalised, with its maximum and sum, for the joining kernel
+      float* part = scratch + ((((size_t)blockIdx.x * G + g) * Z + zi) * WPM_QT + row) * (vd + 2);
+      part[d] = acc;
+      if (d == 0) {
+        part[vd] = m_all;
+        part[vd + 1] = l_all;
+      }
+    } else {
+      fin[idx] = acc / l_all;
+    }
   }
+  if (Z > 1) return;
   __syncthreads();
   for (int idx = tid; idx < n_rows * vd; idx += blockDim.x) {
     const int row = idx / vd, d = idx - row * vd;
@@ -400,6 +417,64 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
   }
 }
 
+// Joins what the blocks that shared a few-row tile's stages left in scratch memory, turns the
+// rows back by their positions and stores them.  One block per (tile, key/value head).
+__global__ void wp_attention_join_kernel(const float* __restrict__ scratch, const int* __restrict__ positions,
+                                         const int* __restrict__ cu_q, int n_seqs, bf16* __restrict__ out,
+                                         int out_stride, int H, int G, int vd, int warps, int key_splits,
+                                         const float* __restrict__ freq_v) {
+  extern __shared__ float join_s[];   // [rows][vd]
+  int seq = -1, t0 = 0, nq = 0;
+  {
+    int b = blockIdx.x;
+    for (int s = 0; s < n_seqs; ++s) {
+      const int a = cu_q[s], e = cu_q[s + 1];
+      const int nt = (e - a + WPM_QT - 1) / WPM_QT;
+      if (b < nt) {
+        seq = s;
+        t0 = a + b * WPM_QT;
+        nq = min(WPM_QT, e - t0);
+        break;
+      }
+      b -= nt;
+    }
+  }
+  const int g = blockIdx.y, Hg = H / G;
+  if (seq < 0 || !(warps > 1 && nq * Hg <= WPM_QT)) return;   // not a tile that was shared out
+  const int n_rows = nq * Hg, vhalf = vd >> 1, Z = key_splits;
+  const int p0 = positions[t0];
+  pdl_wait();
+  pdl_trigger();
+  const float* base = scratch + (((size_t)blockIdx.x * G + g) * Z) * WPM_QT * (vd + 2);
+  for (int idx = threadIdx.x; idx < n_rows * vd; idx += blockDim.x) {
+    const int row = idx / vd, d = idx - row * vd;
+    float m_all = -INFINITY;
+    for (int z = 0; z < Z; ++z) m_all = fmaxf(m_all, base[((size_t)z * WPM_QT + row) * (vd + 2) + vd]);
+    float l_all = 0.0f, acc = 0.0f;
+    for (int z = 0; z < Z; ++z) {   // fixed order
+      const float* part = base + ((size_t)z * WPM_QT + row) * (vd + 2);
+      const float f = part[vd] == -INFINITY ? 0.0f : __expf(part[vd] - m_all);
+      l_all = fmaf(part[vd + 1], f, l_all);
+      acc = fmaf(part[d], f, acc);
+    }
+    join_s[idx] = acc / l_all;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n_rows * vd; idx += blockDim.x) {
+    const int row = idx / vd, d = idx - row * vd;
+    const int tok = row / Hg, h = g * Hg + row % Hg;
+    float x = join_s[idx];
+    if (freq_v) {
+      const int fi = d < vhalf ? d : d - vhalf;
+      float sn, cs;
+      sincosf((float)(p0 + tok) * freq_v[fi], &sn, &cs);
+      const float y = join_s[row * vd + (d < vhalf ? d + vhalf : d - vhalf)];
+      x = d < vhalf ? x * cs + y * sn : x * cs - y * sn;
+    }
+    out[(size_t)(t0 + tok) * out_stride + (size_t)h * vd + d] = __float2bfloat16_rn(x);
+  }
+}
+
 }  // namespace si
 
 template <int KD16, int VD8>
@@ -408,7 +483,8 @@ static int launch_wp_attention_mma(const void* q, int q_stride, const int* posit
                                    int tok_table_stride, si::PlanesLayout tl, const void* blk_pool,
                                    const int* blk_table, int blk_table_stride, si::PlanesLayout bl,
                                    void* out, int out_stride, int n_tokens, int H, float scale, int W,
-                                   int P, const float* freq_v, cudaStream_t stream) {
+                                   int P, const float* freq_v, int key_splits, float* scratch,
+                                   cudaStream_t stream) {
   const int Hg = H / tl.kv_heads;
   const int warps = Hg < si::WPM_MAX_WARPS ? Hg : si::WPM_MAX_WARPS;
   const size_t stages = (size_t)si::WPM_NST * si::WPM_KT * (tl.kd + tl.vd + 2 * si::WPM_PAD) * sizeof(si::bf16);
@@ -418,10 +494,19 @@ static int launch_wp_attention_mma(const void* q, int q_stride, const int* posit
   auto kern = si::wp_attention_mma_kernel<KD16, VD8>;
   if (smem > 48 * 1024) SI_ALLOW_DYNAMIC_SMEM(kern, smem);
   // an upper bound of the tiles: every sequence's last tile may be short
-  dim3 grid((n_tokens + si::WPM_QT - 1) / si::WPM_QT + n_seqs, tl.kv_heads, (Hg + warps - 1) / warps);
+  const int chunks = (Hg + warps - 1) / warps;
+  dim3 grid((n_tokens + si::WPM_QT - 1) / si::WPM_QT + n_seqs, tl.kv_heads,
+            chunks > key_splits ? chunks : key_splits);
   SI_LAUNCH(kern, grid, 32 * warps, smem, stream, (const si::bf16*)q, q_stride, positions, cu_q, n_seqs,
             (const si::bf16*)tok_pool, tok_table, tok_table_stride, tl, (const si::bf16*)blk_pool,
-            blk_table, blk_table_stride, bl, (si::bf16*)out, out_stride, H, scale, W, P, freq_v);
+            blk_table, blk_table_stride, bl, (si::bf16*)out, out_stride, H, scale, W, P, freq_v,
+            key_splits, scratch);
+  if (key_splits > 1) {
+    dim3 jgrid(grid.x, tl.kv_heads);
+    SI_LAUNCH(si::wp_attention_join_kernel, jgrid, 128, (size_t)si::WPM_QT * tl.vd * sizeof(float), stream,
+              (const float*)scratch, positions, cu_q, n_seqs, (si::bf16*)out, out_stride, H, tl.kv_heads,
+              tl.vd, warps, key_splits, freq_v);
+  }
   return SI_OK;
 }
 
@@ -431,12 +516,17 @@ SI_API int si_wp_attention_mma_fits(int kd, int vd) {
 }
 
 // Arguments as si_wp_attention, plus the sequences' token ranges cu_q[0..n_seqs]; bfloat16.
+// key_splits > 1: tiles of few rows (tokens x heads of a group <= 16) are shared out among that
+// many blocks and joined by a second kernel; scratch then holds
+// (ceil(n_tokens / 16) + n_seqs) * G * key_splits * 16 * (vd + 2) floats.
 SI_API int si_wp_attention_mma(const void* q, int q_stride, const int* positions, const int* cu_q,
                                int n_seqs, const void* tok_pool, const int* tok_table,
                                int tok_table_stride, int tok_rows, const void* blk_pool,
                                const int* blk_table, int blk_table_stride, int blk_rows, void* out,
                                int out_stride, int n_tokens, int H, int G, int kd, int vd, float scale,
-                               int W, int P, const float* freq_v, cudaStream_t stream) {
+                               int W, int P, const float* freq_v, int key_splits, float* scratch,
+                               cudaStream_t stream) {
+  if (key_splits < 1 || key_splits > 16 || (key_splits > 1 && !scratch)) return SI_ERR_ARG;
   if (!q || !positions || !cu_q || !tok_pool || !tok_table || !out || n_tokens < 0 || n_seqs < 0 ||
       H <= 0 || G <= 0 || H % G != 0 || tok_rows <= 0)
     return SI_ERR_ARG;
@@ -453,7 +543,7 @@ SI_API int si_wp_attention_mma(const void* q, int q_stride, const int* positions
     return launch_wp_attention_mma<KD16, VD8>(q, q_stride, positions, cu_q, n_seqs, tok_pool,       \
                                               tok_table, tok_table_stride, tl, blk_pool, blk_table, \
                                               blk_table_stride, bl, out, out_stride, n_tokens, H,   \
-                                              scale, W, P, freq_v, stream);
+                                              scale, W, P, freq_v, key_splits, scratch, stream);
   SI_WPM_CASE(4, 8)
   SI_WPM_CASE(4, 16)
   SI_WPM_CASE(8, 16)

@@ -697,7 +697,8 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
                           blk_rows: int, out: torch.Tensor, num_q_heads: int, num_kv_heads: int,
                           key_dim: int, value_dim: int, scale: float, window: int | None,
                           pool_size: int | None, freq_v: torch.Tensor | None,
-                          cu_q: torch.Tensor | None = None, n_seqs: int = 0) -> torch.Tensor:
+                          cu_q: torch.Tensor | None = None, n_seqs: int = 0, key_splits: int = 1,
+                          scratch: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of every token over the last ``window`` tokens of its request and the pooled
     blocks wholly before them, one softmax over both; each head's output is turned back by the
     query's position (``freq_v``; None leaves it).  ``q`` may be the fused projection buffer:
@@ -705,9 +706,17 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
 
     bfloat16 with head sizes that are multiples of 16 up to 128, and the sequences' token
     ranges given (``cu_q``, ``n_seqs``): the tensor-core kernel, tiles of 16 tokens of a
-    sequence, float32 scores and sums.  Otherwise (float32 models, other sizes): the generic
-    kernel, float32 arithmetic throughout."""
+    sequence, float32 scores and sums; with ``key_splits`` > 1 (see ``window_pool_key_splits``)
+    tiles of a token or two are shared out among that many blocks, which meet in ``scratch``
+    (float32, ``window_pool_scratch_rows`` rows of ``value_dim + 2``).  Otherwise (float32 models,
+    other sizes): the generic kernel, float32 arithmetic throughout."""
     _dev(positions, tok_seq, tok_pool, tok_table, blk_pool, blk_table, out, freq_v, cu_q)
+    if key_splits > 1:
+        _dev(scratch)
+        need = window_pool_scratch_rows(out.shape[0], n_seqs, num_kv_heads, key_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.dim() != 2 or \
+                scratch.shape[1] != value_dim + 2 or scratch.shape[0] < need:
+            raise KernelError("window_pool_attention: scratch too small for the key splits")
     if q.dtype == torch.bfloat16 and cu_q is not None and n_seqs > 0 and q.is_cuda and \
             q.stride(1) == 1 and tok_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and \
             out.shape[1] == num_q_heads * value_dim and q.stride(0) % 2 == 0 and \
@@ -719,7 +728,8 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
             tok_table.stride(0), tok_rows, _p(blk_pool), _p(blk_table),
             0 if blk_table is None else blk_table.stride(0), blk_rows, _p(out), out.stride(0),
             out.shape[0], num_q_heads, num_kv_heads, key_dim, value_dim, _c_float(scale),
-            int(window or 0), int(pool_size or 0), _p(freq_v), _stream()), "window_pool_attention_mma")
+            int(window or 0), int(pool_size or 0), _p(freq_v), key_splits, _p(scratch), _stream()),
+            "window_pool_attention_mma", kernels=2 if key_splits > 1 else 1)
         return out
     if not q.is_cuda or q.stride(1) != 1 or q.dtype != tok_pool.dtype or out.dtype != q.dtype:
         raise KernelError("window_pool_attention: q, the cache and out must share a dtype; q rows contiguous")
@@ -735,6 +745,28 @@ def window_pool_attention(q: torch.Tensor, positions: torch.Tensor, tok_seq: tor
         num_q_heads, num_kv_heads, key_dim, value_dim, _c_float(scale), int(window or 0),
         int(pool_size or 0), _p(freq_v), _dt(q), _stream()), "window_pool_attention")
     return out
+
+
+WINDOW_POOL_SPLIT_MAX_TOKENS = 64   # steps up to this size may share a tile's keys out among blocks
+WINDOW_POOL_MAX_SPLITS = 8
+
+
+def window_pool_key_splits(n_tokens: int, n_seqs: int, num_kv_heads: int, window: int | None,
+                           pool_size: int | None, max_kv_len: int) -> int:
+    """Among how many blocks a small step (decoding) shares each tile's stages of 64 keys: enough
+    blocks for two an SM, no more than half the stages a tile has."""
+    if n_tokens > WINDOW_POOL_SPLIT_MAX_TOKENS or n_seqs <= 0:
+        return 1
+    keys = min(window, max_kv_len) if window else max_kv_len
+    if window and pool_size:
+        keys += max(max_kv_len - window, 0) // pool_size
+    stages = max(1, (keys + 63) // 64)
+    want = -(-2 * 148 // (n_seqs * num_kv_heads))
+    return max(1, min(want, stages // 2, WINDOW_POOL_MAX_SPLITS))
+
+
+def window_pool_scratch_rows(n_tokens: int, n_seqs: int, num_kv_heads: int, key_splits: int) -> int:
+    return ((n_tokens + 15) // 16 + n_seqs) * num_kv_heads * key_splits * 16
 
 
 # ------------------------------------------------------ generalised delta rule

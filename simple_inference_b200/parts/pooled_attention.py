@@ -119,9 +119,20 @@ class PooledWindowAttention(Mixer):
                                           blk_pool, blk_table, blk_rows, n, self.num_kv_heads,
                                           self.key_dim, self.value_dim, self.pool)
         mixed = ctx.ws.get("wpattn.mixed", (n, self.out_width), x.dtype)
+        splits, scratch = 1, None
+        if x.dtype == torch.bfloat16:   # a decode step has too few tiles for the GPU: share their keys out
+            splits = ops.window_pool_key_splits(n, ctx.n_seqs, self.num_kv_heads, self.window, self.pool,
+                                                ctx.max_kv_len)
+            if splits > 1:
+                most = ops.window_pool_scratch_rows(ops.WINDOW_POOL_SPLIT_MAX_TOKENS,
+                                                    ops.WINDOW_POOL_SPLIT_MAX_TOKENS, self.num_kv_heads,
+                                                    ops.WINDOW_POOL_MAX_SPLITS)
+                scratch = ctx.ws.get("wpattn.parts", (most, self.value_dim + 2), torch.float32,
+                                     row_cap=most)
         ops.window_pool_attention(qkv, ctx.positions, ctx.tok_seq, tok.pool, tok_table, tok_rows,
                                   blk_pool, blk_table, blk_rows, mixed, self.num_heads,
                                   self.num_kv_heads, self.key_dim, self.value_dim, self.scale,
-                                  self.window, self.pool, self.freq_v, ctx.cu_q, ctx.n_seqs)
+                                  self.window, self.pool, self.freq_v, ctx.cu_q, ctx.n_seqs, splits,
+                                  scratch)
         return ops.linear_for_residual(mixed, self.w_o, ctx.ws, "wpattn.proj",
                                        getattr(ctx, "partial_sums_ok", False))

@@ -266,16 +266,23 @@ def test_tensor_core_attention_equals_the_generic_kernel(H, G, kd, vd, W, P):
     dev = {k: (v.to(torch.bfloat16).cuda() if v.dtype == torch.float32 else v.cuda())
            for k, v in case.items() if isinstance(v, torch.Tensor)}
     outs = []
-    for cu_q in (None, dev["cu_q"]):
+    for cu_q, splits in ((None, 1), (dev["cu_q"], 1), (dev["cu_q"], 3), (dev["cu_q"], 8)):
         out = torch.zeros(n, H * vd, dtype=torch.bfloat16, device="cuda")
+        scratch = None
+        if splits > 1:   # tiles of few rows shared out among blocks, joined by a second kernel
+            scratch = torch.full((ops.window_pool_scratch_rows(n, len(seqs), G, splits), vd + 2),
+                                 float("nan"), device="cuda")
         ops.window_pool_attention(q, dev["positions"], dev["tok_seq"], dev["tok_pool"], dev["tok_table"],
                                   case["rows"], dev["blk_pool"], dev["blk_table"], case["blk_rows"], out,
-                                  H, G, kd, vd, 0.6 / kd ** 0.5 * 4, W, P, freq_v, cu_q, len(seqs))
+                                  H, G, kd, vd, 0.6 / kd ** 0.5 * 4, W, P, freq_v, cu_q, len(seqs),
+                                  splits, scratch)
         outs.append(out.float().cpu())
-    generic, fast = outs
-    assert torch.isfinite(fast).all() and generic.abs().max() < 100   # nobody read a poisoned page
-    assert (fast - generic).abs().max() < 0.04 * generic.abs().max()
-    assert relative_error(fast, generic) < 0.03
+    generic = outs[0]
+    assert generic.abs().max() < 100   # nobody read a poisoned page
+    for fast in outs[1:]:
+        assert torch.isfinite(fast).all()
+        assert (fast - generic).abs().max() < 0.04 * generic.abs().max()
+        assert relative_error(fast, generic) < 0.03
 
 
 @pytest.mark.parametrize("rows", [1, 9, 16, 40, 130, 300])
