@@ -291,8 +291,8 @@ delta_recurrence_kernel(const float* __restrict__ prep, const int* __restrict__ 
   }
 }
 
-// One block per token; a warp takes heads in turn: the head's mean square over its D channels is
-// a sum within the warp, in a fixed order.
+// A block per token and eight heads, a warp per head: the head's mean square over its D channels
+// is a sum within the warp, in a fixed order.
 constexpr int DELTA_OUT_WARPS = 8;
 
 template <typename T, typename TW>
@@ -306,7 +306,8 @@ delta_output_kernel(const float* __restrict__ o, const T* __restrict__ proj, int
   const float* orow = o + (size_t)t * HD;
   const T* grow = proj + (size_t)t * proj_stride + 3 * HD;
   T* yrow = out + (size_t)t * HD;
-  for (int h = warp; h < heads; h += DELTA_OUT_WARPS) {
+  const int h = blockIdx.y * DELTA_OUT_WARPS + warp;
+  if (h < heads) {
     float ss = 0.0f;
     for (int c = lane; c < D; c += 32) {
       const float x = orow[h * D + c];
@@ -403,16 +404,18 @@ SI_API int si_delta_output(const float* o, const void* proj, int proj_stride, co
     return SI_ERR_ARG;
   if (n_tokens == 0) return SI_OK;
   const int threads = 32 * si::DELTA_OUT_WARPS;
+  if (heads > 65535 * si::DELTA_OUT_WARPS) return SI_ERR_TOO_LARGE;
+  const dim3 grid(n_tokens, (heads + si::DELTA_OUT_WARPS - 1) / si::DELTA_OUT_WARPS);
   if (dtype == SI_BF16 && gain_dtype == SI_BF16)
-    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, __nv_bfloat16>), grid, threads, 0, stream, o,
               (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)gain, (__nv_bfloat16*)out,
               heads, D, eps);
   else if (dtype == SI_BF16 && gain_dtype == SI_F32)
-    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, float>), n_tokens, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<__nv_bfloat16, float>), grid, threads, 0, stream, o,
               (const __nv_bfloat16*)proj, proj_stride, (const float*)gain, (__nv_bfloat16*)out, heads,
               D, eps);
   else if (dtype == SI_F32 && gain_dtype == SI_F32)
-    SI_LAUNCH((si::delta_output_kernel<float, float>), n_tokens, threads, 0, stream, o,
+    SI_LAUNCH((si::delta_output_kernel<float, float>), grid, threads, 0, stream, o,
               (const float*)proj, proj_stride, (const float*)gain, (float*)out, heads, D, eps);
   else
     return SI_ERR_DTYPE;
