@@ -1,5 +1,6 @@
 // Window attention with pooled blocks on the tensor cores (bfloat16 storage, mma.sync
-// m16n8k16 with float32 accumulation; scores, softmax and the output sums are float32).
+// m16n8k16 with float32 accumulation; scores, softmax and the output sums are float32, and the
+// softmax weights enter the second product as two bfloat16 terms).
 //
 // A block works one tile of 16 consecutive tokens of one sequence for one key/value head; each
 // of its warps is one query head of that group, so the group's heads share every key and value
@@ -294,11 +295,17 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
 #pragma unroll
       for (int kk = 0; kk < WPM_KT / 16; ++kk) {
         if (!((own >> kk) & 1)) continue;
-        uint32_t pa[4];
-        pa[0] = wpm_pack(s[2 * kk][0], s[2 * kk][1]);
-        pa[1] = wpm_pack(s[2 * kk][2], s[2 * kk][3]);
-        pa[2] = wpm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        pa[3] = wpm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        // the weights as two bfloat16 terms, p = hi + lo: what the tensor cores multiply keeps 16
+        // bits of the float32 weight instead of 8
+        uint32_t pa[4], pb[4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const float w0 = s[2 * kk + (f >> 1)][(f & 1) * 2], w1 = s[2 * kk + (f >> 1)][(f & 1) * 2 + 1];
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(w0, w1);
+          const float2 back = __bfloat1622float2(hi);
+          pa[f] = *reinterpret_cast<const uint32_t*>(&hi);
+          pb[f] = wpm_pack(w0 - back.x, w1 - back.y);
+        }
         const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
         for (int n2 = 0; n2 < VD8 / 2; ++n2) {
@@ -308,6 +315,8 @@ wp_attention_mma_kernel(const bf16* __restrict__ q, int q_stride, const int* __r
             wpm_ldmatrix_x4_trans(b, (unsigned)__cvta_generic_to_shared(vp));
             wpm_mma(o[2 * n2], pa, b[0], b[1]);
             wpm_mma(o[2 * n2 + 1], pa, b[2], b[3]);
+            wpm_mma(o[2 * n2], pb, b[0], b[1]);
+            wpm_mma(o[2 * n2 + 1], pb, b[2], b[3]);
           }
         }
       }

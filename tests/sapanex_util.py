@@ -21,7 +21,7 @@ from safetensors.torch import save_file
 def attention_layer(dim=16, heads=4, kv_heads=2, vdim=24, window=12, pool=4, rot_dims=8,
                     base=10000.0, scaling=None, scale=None, ff=None):
     mixer = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "vdim": vdim,
-             "mask": {"size": window, "pool": pool},
+             "mask": {"size": window, "pool": pool} if window else None,
              "rot": {"base": base, "dims": rot_dims, "scaling": scaling},
              "scale": scale if scale is not None else 3.0 / dim ** 0.5}
     return {"type": "attention", "mixer": mixer,

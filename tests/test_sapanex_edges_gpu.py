@@ -140,6 +140,24 @@ def test_other_sizes_and_values_that_happen_to_be_one(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_without_a_window_sees_everything(tmp_path, dtype):
+    """No mask in the configuration: every earlier token is seen, nothing is pooled, the token
+    cache keeps all its pages (head sizes the tensor-core kernel takes, so bfloat16 runs it)."""
+    cfg = config([attention_layer(dim=32, heads=4, kv_heads=2, vdim=32, window=None, pool=None,
+                                  rot_dims=16, scale=0.8, ff=40), delta_layer()], width=48, vocab=43)
+    assert cfg["layers"][0]["mixer"]["mask"] is None
+    w = make_weights(cfg, 4)
+    folder = write_model(tmp_path, cfg, w)
+    toks = tokens(150, cfg["vocab"], 6)
+    want = oracle(cfg, w, toks)
+    d = Driver(folder, dtype)
+    tol = FP32_TOL if dtype == "float32" else BF16_TOL
+    assert relative_error(d.run_cut("a", toks, [150]), want) < tol
+    assert relative_error(d.run_cut("a", toks, [70, 1, 1, 33, 1]), want) < tol
+    assert all(p >= 0 for p in d.cache.block_table("a", 0)) if d.cache.is_admitted("a") else True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(tmp_path, dtype):
     """``InferenceEngine``: scheduler, portions of prompts, continuous batching, sampling."""
     from simple_inference_b200.engine.engine import InferenceEngine

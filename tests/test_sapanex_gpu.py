@@ -251,7 +251,8 @@ def _paged_case(G, kd, vd, W, P, seqs, seed, rows=16, blk_rows=4):
 
 
 @pytest.mark.parametrize("H,G,kd,vd,W,P", [(8, 2, 64, 80, 40, 8), (3, 1, 128, 128, 24, 5),
-                                             (10, 2, 16, 32, 7, 16), (4, 4, 32, 16, 100, 3)])
+                                             (10, 2, 16, 32, 7, 16), (4, 4, 32, 16, 100, 3),
+                                             (20, 1, 32, 32, 50, 4), (6, 3, 48, 96, 2000, 64)])
 def test_tensor_core_attention_equals_the_generic_kernel(H, G, kd, vd, W, P):
     """Portions of prompts (from position 0, in mid-sequence, over page borders), single decoded
     tokens and a first token in one batch; bfloat16 caches; the generic kernel, which the other
