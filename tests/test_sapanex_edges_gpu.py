@@ -197,3 +197,26 @@ def test_trace_replay_of_a_sapanex_folder(tmp_path):
         assert t.step([("b", b[64:], [])], end=["b"]) is None
         got = t.step([("a", a[51:], [38]), ("c", b[:3], [2])], end=["a", "c"])
         assert relative_error(got, torch.stack([wa[89], wb[2]])) < FP32_TOL
+
+
+def test_command_line_generates_from_a_sapanex_folder(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = config([delta_layer(ff=32), attention_layer(window=12, pool=4, ff=48)], width=48, vocab=59)
+    w = make_weights(cfg, 23)
+    folder = write_model(tmp_path / "model", cfg, w)
+    prompt = tokens(21, cfg["vocab"], 8)
+    want, seq = [], list(prompt)
+    for _ in range(6):
+        want.append(int(oracle(cfg, w, seq)[-1].argmax()))
+        seq.append(want[-1])
+    out = subprocess.run(
+        [sys.executable, str(root / "generate.py"), "--model", str(folder), "--dtype", "float32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--temperature", "0",
+         "--eos-id", "-1", "--max-seq-len", "64", "--block-size", "4"],
+        capture_output=True, text=True, cwd=str(root), timeout=600)
+    assert out.returncode == 0, out.stderr
+    assert json.loads(out.stdout.strip().splitlines()[-1])["tokens"] == want
