@@ -71,12 +71,44 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride
   float z[TG];
 #pragma unroll
   for (int tt = 0; tt < TG; ++tt) z[tt] = z0;
+  // z = z0 + sum_l W2[c,l] low_l: term l goes to running sum l mod 4, the four are joined as
+  // (0+1)+(2+3), whatever the number of tokens a block takes, so a token's decay does not depend
+  // on whether it came alone (decoding) or in a prompt
+  float zz[TG][4];
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt) zz[tt][0] = zz[tt][1] = zz[tt][2] = zz[tt][3] = 0.0f;
+  int l = 0;
+  auto four = [&]() {   // terms l .. l+3 of every token
+    float w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = to_f32<T>(w2t[(size_t)(l + j) * HD + col]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int tt = 0; tt < TG; ++tt) zz[tt][j] = __fmaf_rn(w[j], low_s[tt * L + l + j], zz[tt][j]);
+  };
+  if (TG == 1) {
+    // one token: the block's time is the trips to memory for the decay matrix's words, so
+    // thirty-two of them are asked for at once
 #pragma unroll 8
-  for (int l = 0; l < L; ++l) {
+    for (; l + 4 <= L; l += 4) four();
+  } else {
+#pragma unroll 2
+    for (; l + 4 <= L; l += 4) four();
+  }
+  for (int j = 0; l < L; ++l, ++j) {   // up to three left over: they are terms 0, 1, 2 mod 4
     const float w = to_f32<T>(w2t[(size_t)l * HD + col]);
 #pragma unroll
-    for (int tt = 0; tt < TG; ++tt) z[tt] = fmaf(w, low_s[tt * L + l], z[tt]);
+    for (int tt = 0; tt < TG; ++tt) {
+      const float x = low_s[tt * L + l];   // explicit fused operations: the same in every instantiation
+      if (j == 0) zz[tt][0] = __fmaf_rn(w, x, zz[tt][0]);
+      else if (j == 1) zz[tt][1] = __fmaf_rn(w, x, zz[tt][1]);
+      else zz[tt][2] = __fmaf_rn(w, x, zz[tt][2]);
+    }
   }
+#pragma unroll
+  for (int tt = 0; tt < TG; ++tt)
+    z[tt] = __fadd_rn(z[tt], __fadd_rn(__fadd_rn(zz[tt][0], zz[tt][1]), __fadd_rn(zz[tt][2], zz[tt][3])));
 #pragma unroll
   for (int tt = 0; tt < TG; ++tt) {
     if (tt < nt) {

@@ -151,8 +151,8 @@ def test_float32_does_not_depend_on_the_cut(models):
     toks = tokens(90, cfg["vocab"], 31)
     d = Driver(folder, "float32")
     whole = d.run_cut("a", toks, [len(toks)])
-    for cuts in ([1], [2], [7, 3]):
-        assert relative_error(d.run_cut("a", toks, cuts), whole) < 2e-6
+    for cuts in ([1], [2], [7, 3], [64, 1], [70, 20]):   # below and above the row counts where kernels change
+        assert relative_error(d.run_cut("a", toks, cuts), whole) < 1e-7   # measured 0.0: the same sums in the same order
 
 
 # --------------------------------------------------------------- batches and reuse
